@@ -1,0 +1,23 @@
+"""flash-llm_b200 — B200-native Load-as-Sparse / Compute-as-Dense SpMM behind Flash-LLM's SpMM_API interface.
+
+The product is ``build/libSpMM_API.so`` (sources under ``csrc/``).  This package is its thin Python host
+side: it loads the library through its C ABI and mirrors the reference's operator names.  There is no
+fallback: if the library is missing or cannot be loaded, importing :mod:`api` members raises.
+"""
+from .api import (  # noqa: F401
+    LIBRARY_PATH,
+    FlashLLMError,
+    GenSparseMatrixBinFile,
+    InitSparseMatrixA_API,
+    InitSparseMatrixA_API_NoReorder,
+    SpMM_SplitK_API,
+    build_library,
+    consume_status,
+    encode_on_device,
+    get_plan,
+    launch_count,
+    library,
+    set_plan,
+    splitk_reduction,
+)
+from . import synthetic  # noqa: F401

@@ -1,0 +1,174 @@
+"""ctypes host side of ``libSpMM_API.so``, mirroring the reference's operator interface
+(Flash-LLM build/SpMM_API.cuh:38-67): same names, argument order and meaning.
+
+Device buffers are passed as integer device pointers (e.g. ``tensor.data_ptr()``); torch is only the
+owner of device memory and streams in the callers, never part of a signature here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(_PKG)
+LIBRARY_PATH = os.path.join(_ROOT, "build", "libSpMM_API.so")
+
+_u32p = C.POINTER(C.c_uint32)
+_i32p = C.POINTER(C.c_int)
+
+
+class FlashLLMError(RuntimeError):
+    """A library call returned a CUDA error code or the library is unavailable."""
+
+
+def build_library(verbose: bool = False) -> str:
+    """Compile ``build/libSpMM_API.so`` for sm_100a with nvcc (no GPU needed)."""
+    cmd = ["make", "-C", os.path.join(_PKG, "csrc")] + ([] if verbose else ["-s"])
+    subprocess.run(cmd, check=True)
+    return LIBRARY_PATH
+
+
+_lib = None
+
+
+def library() -> C.CDLL:
+    """The loaded library; raises :class:`FlashLLMError` when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIBRARY_PATH):
+        raise FlashLLMError(
+            f"{LIBRARY_PATH} is missing: build it with `make -C flash-llm_b200/csrc` "
+            "(or __graft_entry__.build()); there is no fallback implementation")
+    L = C.CDLL(LIBRARY_PATH)
+    L.FlashLLM_SpMM_SplitK.restype = C.c_int
+    L.FlashLLM_SpMM_SplitK.argtypes = [C.c_void_p] * 3 + [C.c_void_p] * 3 + [C.c_int] * 3 + [C.c_void_p, C.c_int]
+    for name in ("FlashLLM_InitSparseMatrixA", "FlashLLM_InitSparseMatrixA_NoReorder"):
+        f = getattr(L, name)
+        f.restype = C.c_int
+        f.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(_u32p), C.POINTER(_i32p)]
+    L.FlashLLM_Free.argtypes = [C.c_void_p]
+    L.GenSparseMatrixBinFile.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_char_p, C.c_char_p, C.c_char_p]
+    L.FlashLLM_EncodeOnDevice_TileOffsets.restype = C.c_int
+    L.FlashLLM_EncodeOnDevice_TileOffsets.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    L.FlashLLM_EncodeOnDevice_Pack.restype = C.c_int
+    L.FlashLLM_EncodeOnDevice_Pack.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                               C.c_int]
+    L.FlashLLM_SplitK_Reduction.restype = C.c_int
+    L.FlashLLM_SplitK_Reduction.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    L.FlashLLM_SetPlan.argtypes = [C.c_int] * 7
+    L.FlashLLM_GetPlan.restype = C.c_int
+    L.FlashLLM_GetPlan.argtypes = [C.c_int] * 4 + [_i32p]
+    L.FlashLLM_ConsumeStatus.restype = C.c_uint
+    L.FlashLLM_LaunchCount.restype = C.c_ulonglong
+    _lib = L
+    return L
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise FlashLLMError(f"{what} failed with cudaError_t {code}")
+
+
+# ----------------------------------------------------------------------------- encoders (host)
+
+def _encode_host(A_h: np.ndarray, reorder: bool) -> tuple[np.ndarray, np.ndarray, int]:
+    if A_h.dtype == np.float16:
+        A_h = A_h.view(np.uint16)
+    if A_h.dtype != np.uint16 or A_h.ndim != 2:
+        raise TypeError("A_h must be a 2-D float16 (or uint16 bit pattern) array")
+    A_h = np.ascontiguousarray(A_h)
+    M, K = A_h.shape
+    L = library()
+    fn = L.FlashLLM_InitSparseMatrixA if reorder else L.FlashLLM_InitSparseMatrixA_NoReorder
+    comp_p, offs_p = _u32p(), _i32p()
+    n = fn(A_h.ctypes.data, M, 0, K, C.byref(comp_p), C.byref(offs_p))
+    if n < 0:
+        raise FlashLLMError({-1: f"M={M} must be a positive multiple of 128 and K={K} of 64",
+                             -2: "out of host memory", -3: "matrix too large for 32-bit TileOffsets"}.get(n, str(n)))
+    offs = np.ctypeslib.as_array(offs_p, shape=(n,)).copy()
+    words = int(offs[-1]) * 4
+    comp = np.ctypeslib.as_array(comp_p, shape=(max(words, 1),))[:words].copy()
+    L.FlashLLM_Free(C.cast(comp_p, C.c_void_p))
+    L.FlashLLM_Free(C.cast(offs_p, C.c_void_p))
+    return comp, offs, n
+
+
+def InitSparseMatrixA_API(A_h: np.ndarray, M: int | None = None, N: int = 0, K: int | None = None):
+    """Dense fp16 ``A_h[M][K]`` -> ``(Compressed_A uint32[NNZ], TileOffsets int32[NumOffsets], NumOffsets)``,
+    bit-identical to the reference encoder (csrc/SpMM_API.cu:163-360).  ``N`` is ignored, as there."""
+    del N
+    if M is not None and K is not None:
+        A_h = np.asarray(A_h).reshape(M, K)
+    return _encode_host(A_h, True)
+
+
+def InitSparseMatrixA_API_NoReorder(A_h: np.ndarray, M: int | None = None, N: int = 0, K: int | None = None):
+    """Scan-order variant (reference csrc/SpMM_API.cu:363-489)."""
+    del N
+    if M is not None and K is not None:
+        A_h = np.asarray(A_h).reshape(M, K)
+    return _encode_host(A_h, False)
+
+
+def GenSparseMatrixBinFile(dense_file: str, M: int, K: int, nz_weights_file: str, tile_offsets_file: str,
+                           output_sizes_file: str) -> None:
+    """File-to-file conversion (reference csrc/SpMM_API.cu:500-555), byte-compatible outputs."""
+    library().GenSparseMatrixBinFile(dense_file.encode(), M, K, nz_weights_file.encode(), tile_offsets_file.encode(),
+                                     output_sizes_file.encode())
+
+
+# ----------------------------------------------------------------------------- device entry points
+
+def SpMM_SplitK_API(stream: int, A: int | None, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int,
+                    N: int, K: int, Reduction_Workspace: int | None, Split_K: int) -> None:
+    """Enqueue ``C[N][M] = B[N][K] @ A[M][K]^T`` on ``stream`` (reference csrc/SpMM_API.cu:55-130).
+    All buffer arguments are integer device pointers; ``A`` is unused and may be ``None``."""
+    code = library().FlashLLM_SpMM_SplitK(stream, A, Compressed_A, TileOffsets, B, C_out, M, N, K,
+                                          Reduction_Workspace, Split_K)
+    _check(code, f"SpMM_SplitK_API(M={M}, N={N}, K={K}, Split_K={Split_K})")
+
+
+def splitk_reduction(stream: int, C_out: int, workspace: int, M: int, N: int, split_k: int) -> None:
+    """``C[i] = fp16(sum_s float(workspace[s*M*N + i]))`` (reference csrc/Reduction_Kernel.cuh:24-45)."""
+    _check(library().FlashLLM_SplitK_Reduction(stream, C_out, workspace, M, N, split_k), "SplitK_Reduction")
+
+
+def encode_on_device(stream: int, A_d: int, M: int, K: int, alloc_i32, alloc_u32, read_i32):
+    """Device encoder.  ``alloc_i32(n)`` / ``alloc_u32(n)`` return ``(owner, device_pointer)`` for ``n``
+    elements of device memory, ``read_i32(owner, index)`` reads one int back after synchronising the stream.
+    Returns ``(compressed_owner, offsets_owner, num_offsets, nnz_words)``."""
+    T = (M // 128) * (K // 64)
+    offs_owner, offs_ptr = alloc_i32(T + 2)
+    _check(library().FlashLLM_EncodeOnDevice_TileOffsets(stream, A_d, M, K, offs_ptr), "EncodeOnDevice_TileOffsets")
+    words = int(read_i32(offs_owner, T + 1)) * 4
+    comp_owner, comp_ptr = alloc_u32(max(words, 4))
+    _check(library().FlashLLM_EncodeOnDevice_Pack(stream, A_d, M, K, offs_ptr, comp_ptr, 1), "EncodeOnDevice_Pack")
+    return comp_owner, offs_owner, T + 2, words
+
+
+def set_plan(cluster_k=0, workspace_k=0, a_stages=0, b_stages=0, ring_slots=0, chunk_vectors=0, scatter_warps=0):
+    """Pin the launch plan for later calls (0 = automatic)."""
+    library().FlashLLM_SetPlan(cluster_k, workspace_k, a_stages, b_stages, ring_slots, chunk_vectors, scatter_warps)
+
+
+_PLAN_FIELDS = ("cluster_k", "workspace_k", "a_stages", "b_stages", "ring_slots", "chunk_vectors", "scatter_warps",
+                "smem_bytes")
+
+
+def get_plan(M: int, N: int, K: int, Split_K: int = 1) -> dict:
+    out = (C.c_int * 8)()
+    _check(library().FlashLLM_GetPlan(M, N, K, Split_K, out), "GetPlan")
+    return dict(zip(_PLAN_FIELDS, list(out)))
+
+
+def consume_status() -> int:
+    """Synchronise the device and return-and-clear the kernel status word (0 = healthy)."""
+    return int(library().FlashLLM_ConsumeStatus())
+
+
+def launch_count() -> int:
+    return int(library().FlashLLM_LaunchCount())

@@ -1,0 +1,403 @@
+// Host side of libSpMM_API.so: argument checks, launch-plan choice and kernel launches behind the reference's
+// SpMM_SplitK_API interface (reference csrc/SpMM_API.cu:22-130), plus the C-linkage aliases.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+
+#include "../../include/SpMM_API.cuh"
+#include "spmm_kernel_sm100.cuh"
+#include "tiled_csl_host.h"
+#include "tiling.h"
+
+namespace flashllm {
+
+__device__ unsigned int g_status_word = 0;
+
+static std::atomic<unsigned long long> g_launches{0};
+
+void count_launch()
+{
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// ---------------------------------------------------------------- per-device state
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    std::once_flag once;
+    cudaError_t    init_error = cudaSuccess;
+    int            sm_count   = 0;
+    int            smem_optin = 0;
+    unsigned int*  status     = nullptr;
+};
+
+static DeviceState g_devices[kMaxDevices];
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn  g_encode_tiled = nullptr;
+static std::once_flag g_encode_once;
+
+template<int N_TILE>
+static cudaError_t raise_smem_limit(int bytes)
+{
+    return cudaFuncSetAttribute(spmm_tcgen05_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+static DeviceState* device_state(cudaError_t* err)
+{
+    int dev = 0;
+    *err    = cudaGetDevice(&dev);
+    if (*err != cudaSuccess)
+        return nullptr;
+    if (dev < 0 || dev >= kMaxDevices) {
+        *err = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    DeviceState* st = &g_devices[dev];
+    std::call_once(st->once, [st, dev]() {
+        cudaError_t e = cudaDeviceGetAttribute(&st->sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess)
+            e = cudaDeviceGetAttribute(&st->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (e == cudaSuccess)
+            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->status), g_status_word);
+        // The opt-in limit is a per-device property of each kernel; raise it once instead of on every call
+        // (the reference calls cudaFuncSetAttribute per launch, csrc/SpMM_API.cu:36-37).
+        if (e == cudaSuccess)
+            e = raise_smem_limit<16>(st->smem_optin);
+        if (e == cudaSuccess)
+            e = raise_smem_limit<32>(st->smem_optin);
+        if (e == cudaSuccess)
+            e = raise_smem_limit<64>(st->smem_optin);
+        if (e == cudaSuccess)
+            e = raise_smem_limit<128>(st->smem_optin);
+        st->init_error = e;
+    });
+    *err = st->init_error;
+    return *err == cudaSuccess ? st : nullptr;
+}
+
+int device_status_pointer(unsigned int** status)
+{
+    cudaError_t  err = cudaSuccess;
+    DeviceState* st  = device_state(&err);
+    if (!st)
+        return static_cast<int>(err);
+    *status = st->status;
+    return 0;
+}
+
+static cudaError_t load_encode_tiled()
+{
+    std::call_once(g_encode_once, []() {
+        void*                           fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess
+            && qres == cudaDriverEntryPointSuccess)
+            g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    });
+    return g_encode_tiled ? cudaSuccess : cudaErrorNotSupported;
+}
+
+// ---------------------------------------------------------------- launch plan
+
+struct PlanOverride {
+    int cluster_k = 0, workspace_k = 0, a_stages = 0, b_stages = 0, ring_slots = 0, chunk_vectors = 0, scatter_warps = 0;
+};
+static PlanOverride g_override;
+static std::mutex   g_override_mutex;
+
+static int n_tile_for(int N)
+{
+    return N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : 128));
+}
+
+static int plan_smem_bytes(const SpmmPlan& pl)
+{
+    const int bars = 8 * (2 * pl.ring_slots + 2 * pl.a_stages + 2 * pl.b_stages + 1) + 16;
+    return 1024 /* alignment slack */ + pl.a_stages * kDenseTileBytes + pl.b_stages * pl.n_tile * kTileK * 2
+           + pl.ring_slots * pl.chunk_vectors * 16 + bars;
+}
+
+static bool is_pow2(int v)
+{
+    return v > 0 && (v & (v - 1)) == 0;
+}
+
+// Chooses how to cut K and how deep to pipeline.  Takes the place of the reference's per-N switch over
+// TilingConfig instances (csrc/SpMM_API.cu:79-118) and of its hand-tuned Split_K tables
+// (kernel_benchmark/benchmark.sh:13-15).
+static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Split_K, SpmmPlan* out)
+{
+    PlanOverride ov;
+    {
+        std::lock_guard<std::mutex> lock(g_override_mutex);
+        ov = g_override;
+    }
+    SpmmPlan pl{};
+    pl.n_tile           = n_tile_for(N);
+    const int tile_rows = M / kTileM;
+    const int k_tiles   = K / kTileK;
+    const int n_tiles   = (N + pl.n_tile - 1) / pl.n_tile;
+    const int ctas_flat = tile_rows * n_tiles;
+
+    pl.scatter_warps = ov.scatter_warps ? ov.scatter_warps : 8;
+    pl.chunk_vectors = ov.chunk_vectors ? ov.chunk_vectors : 256;
+    pl.ring_slots    = ov.ring_slots ? ov.ring_slots : (kMaxTileVectors / pl.chunk_vectors + 2);
+    pl.a_stages      = ov.a_stages ? ov.a_stages : 3;
+    pl.b_stages      = ov.b_stages ? ov.b_stages : (pl.n_tile <= 32 ? 4 : 3);
+
+    // Enough CTAs for two per SM and about two waves, but never more K parts than K tiles.
+    const int target = st->sm_count * 4;
+    int       want   = (target + ctas_flat - 1) / ctas_flat;
+    if (want < 1)
+        want = 1;
+    if (want > k_tiles)
+        want = k_tiles;
+    pl.cluster_k = ov.cluster_k ? ov.cluster_k : (want < kMaxClusterK ? want : kMaxClusterK);
+    if (pl.cluster_k > k_tiles)
+        pl.cluster_k = k_tiles;
+    int extra = ov.workspace_k ? ov.workspace_k : (want + pl.cluster_k - 1) / pl.cluster_k;
+    if (extra > Split_K)
+        extra = Split_K;  // the workspace is only promised to hold Split_K partial matrices
+    if (extra * pl.cluster_k > k_tiles)
+        extra = k_tiles / pl.cluster_k;
+    if (extra < 1)
+        extra = 1;
+    if ((static_cast<long long>(M) * N) % 8 != 0)
+        extra = 1;  // the workspace reduction moves eight halves per thread
+    pl.workspace_k = extra;
+    pl.smem_bytes  = plan_smem_bytes(pl);
+
+    const bool ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8) && is_pow2(pl.chunk_vectors)
+                    && pl.chunk_vectors >= 64 && pl.ring_slots <= kMaxRingSlots
+                    && pl.ring_slots * pl.chunk_vectors >= kMaxTileVectors + pl.chunk_vectors
+                    && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
+                    && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK && pl.workspace_k >= 1
+                    && pl.smem_bytes <= st->smem_optin
+                    // the fp32 partial tile of the cluster reduction is parked over the pipeline buffers
+                    && pl.smem_bytes - 2048 >= pl.n_tile * kTileM * 4;
+    if (!ok)
+        return cudaErrorInvalidConfiguration;
+    *out = pl;
+    return cudaSuccess;
+}
+
+template<int N_TILE>
+static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, const SpmmParams& params, int tile_rows,
+                               int n_tiles)
+{
+    const SpmmPlan&     pl = params.plan;
+    cudaLaunchConfig_t  cfg{};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
+    cfg.blockDim         = dim3((kControlWarps + pl.scatter_warps) * 32, 1, 1);
+    cfg.dynamicSmemBytes = pl.smem_bytes;
+    cfg.stream           = stream;
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = pl.cluster_k;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = 1;
+    count_launch();
+    return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
+}
+
+static cudaError_t reduce_workspace(cudaStream_t stream, half* C, const half* ws, long long count, int parts)
+{
+    const int       threads = 256;
+    const long long groups  = (count + 7) / 8;
+    const unsigned  blocks  = static_cast<unsigned>((groups + threads - 1) / threads);
+    count_launch();
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(C, ws, count, parts);
+    return cudaGetLastError();
+}
+
+static bool n_supported(int N)
+{
+    // the reference's dispatch list (csrc/SpMM_API.cu:79-118)
+    return N == 8 || N == 16 || N == 32 || N == 64 || (N > 0 && N % 128 == 0);
+}
+
+}  // namespace flashllm
+
+using namespace flashllm;
+
+cudaError_t SpMM_SplitK_API(cudaStream_t stream,
+                            const half*  A,
+                            const uint4* Compressed_A,
+                            const int*   TileOffsets,
+                            const half*  B,
+                            half*        C,
+                            const int    M_Global,
+                            const int    N_Global,
+                            const int    K_Global,
+                            half*        Reduction_Workspace,
+                            int          Split_K)
+{
+    (void)A;  // kept for signature compatibility; callers pass nullptr
+    if (!n_supported(N_Global)) {
+        printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
+        return cudaErrorUnknown;
+    }
+    if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileM != 0 || K_Global % kTileK != 0 || Split_K < 1
+        || Compressed_A == nullptr || TileOffsets == nullptr || B == nullptr || C == nullptr
+        || (reinterpret_cast<uintptr_t>(Compressed_A) & 15u) != 0 || (reinterpret_cast<uintptr_t>(B) & 15u) != 0
+        || (reinterpret_cast<uintptr_t>(C) & 1u) != 0 || (Split_K > 1 && Reduction_Workspace == nullptr))
+        return cudaErrorInvalidValue;
+
+    cudaError_t  err = cudaSuccess;
+    DeviceState* st  = device_state(&err);
+    if (!st)
+        return err;
+    if ((err = load_encode_tiled()) != cudaSuccess)
+        return err;
+
+    SpmmParams params{};
+    if ((err = make_plan(st, M_Global, N_Global, K_Global, Split_K, &params.plan)) != cudaSuccess)
+        return err;
+    SpmmPlan& pl = params.plan;
+    // A partial-matrix pass needs 16-byte aligned rows of eight halves in both buffers.
+    if (pl.workspace_k > 1
+        && ((reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u) != 0 || (reinterpret_cast<uintptr_t>(C) & 15u) != 0))
+        pl.workspace_k = 1;
+
+    params.compressed   = Compressed_A;
+    params.tile_offsets = TileOffsets;
+    params.out          = pl.workspace_k > 1 ? Reduction_Workspace : C;
+    params.status       = st->status;
+    params.M            = M_Global;
+    params.N            = N_Global;
+    params.K            = K_Global;
+    params.k_tiles      = K_Global / kTileK;
+
+    // B as a 2-D tensor {K (inner), N}; one box = 64 K-elements x n_tile rows, 128-byte swizzle, rows past N read as 0.
+    CUtensorMap      tmap;
+    const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(K_Global), static_cast<cuuint64_t>(N_Global)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K_Global) * 2};
+    const cuuint32_t box[2]     = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(pl.n_tile)};
+    const cuuint32_t estr[2]    = {1, 1};
+    const CUresult   cres       = g_encode_tiled(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(B), dims,
+                                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cres != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+
+    const int tile_rows = M_Global / kTileM;
+    const int n_tiles   = (N_Global + pl.n_tile - 1) / pl.n_tile;
+    switch (pl.n_tile) {
+        case 16: err = launch_spmm<16>(stream, tmap, params, tile_rows, n_tiles); break;
+        case 32: err = launch_spmm<32>(stream, tmap, params, tile_rows, n_tiles); break;
+        case 64: err = launch_spmm<64>(stream, tmap, params, tile_rows, n_tiles); break;
+        default: err = launch_spmm<128>(stream, tmap, params, tile_rows, n_tiles); break;
+    }
+    if (err != cudaSuccess)
+        return err;
+    if (pl.workspace_k > 1)
+        return reduce_workspace(stream, C, Reduction_Workspace, static_cast<long long>(M_Global) * N_Global,
+                                pl.workspace_k);
+    return cudaSuccess;
+}
+
+extern "C" {
+
+int FlashLLM_SpMM_SplitK(void*       stream,
+                         const void* A,
+                         const void* Compressed_A,
+                         const int*  TileOffsets,
+                         const void* B,
+                         void*       C,
+                         int         M,
+                         int         N,
+                         int         K,
+                         void*       Reduction_Workspace,
+                         int         Split_K)
+{
+    return static_cast<int>(SpMM_SplitK_API(static_cast<cudaStream_t>(stream),
+                                            static_cast<const half*>(A),
+                                            static_cast<const uint4*>(Compressed_A),
+                                            TileOffsets,
+                                            static_cast<const half*>(B),
+                                            static_cast<half*>(C),
+                                            M,
+                                            N,
+                                            K,
+                                            static_cast<half*>(Reduction_Workspace),
+                                            Split_K));
+}
+
+int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K)
+{
+    const long long count = static_cast<long long>(M) * N;
+    if (C == nullptr || Reduction_Workspace == nullptr || M <= 0 || N <= 0 || Split_K < 1 || count % 8 != 0
+        || (reinterpret_cast<uintptr_t>(C) & 15u) != 0 || (reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u) != 0)
+        return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(reduce_workspace(static_cast<cudaStream_t>(stream), static_cast<half*>(C),
+                                             static_cast<const half*>(Reduction_Workspace), count, Split_K));
+}
+
+void FlashLLM_SetPlan(int cluster_k, int workspace_k, int a_stages, int b_stages, int ring_slots, int chunk_vectors,
+                      int scatter_warps)
+{
+    std::lock_guard<std::mutex> lock(g_override_mutex);
+    g_override.cluster_k     = cluster_k;
+    g_override.workspace_k   = workspace_k;
+    g_override.a_stages      = a_stages;
+    g_override.b_stages      = b_stages;
+    g_override.ring_slots    = ring_slots;
+    g_override.chunk_vectors = chunk_vectors;
+    g_override.scatter_warps = scatter_warps;
+}
+
+int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out)
+{
+    if (out == nullptr || !n_supported(N) || M <= 0 || K <= 0 || M % kTileM != 0 || K % kTileK != 0 || Split_K < 1)
+        return static_cast<int>(cudaErrorInvalidValue);
+    cudaError_t  err = cudaSuccess;
+    DeviceState* st  = device_state(&err);
+    if (!st)
+        return static_cast<int>(err);
+    SpmmPlan pl{};
+    if ((err = make_plan(st, M, N, K, Split_K, &pl)) != cudaSuccess)
+        return static_cast<int>(err);
+    out[0] = pl.cluster_k;
+    out[1] = pl.workspace_k;
+    out[2] = pl.a_stages;
+    out[3] = pl.b_stages;
+    out[4] = pl.ring_slots;
+    out[5] = pl.chunk_vectors;
+    out[6] = pl.scatter_warps;
+    out[7] = pl.smem_bytes;
+    return 0;
+}
+
+unsigned int FlashLLM_ConsumeStatus(void)
+{
+    cudaError_t  err = cudaSuccess;
+    DeviceState* st  = device_state(&err);
+    if (!st)
+        return 0x80000000u;
+    unsigned int value = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess)
+        return 0x80000000u;
+    if (cudaMemcpy(&value, st->status, sizeof(value), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return 0x80000000u;
+    if (value != 0)
+        cudaMemset(st->status, 0, sizeof(value));
+    return value;
+}
+
+unsigned long long FlashLLM_LaunchCount(void)
+{
+    return g_launches.load(std::memory_order_relaxed);
+}
+
+}  // extern "C"

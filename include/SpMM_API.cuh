@@ -1,0 +1,131 @@
+/*
+ * Public interface of libSpMM_API.so — Load-as-Sparse / Compute-as-Dense SpMM for NVIDIA B200 (sm_100a).
+ *
+ * Drop-in for Flash-LLM's build/SpMM_API.cuh: the first four declarations keep the reference's names,
+ * argument order, C++ linkage and meaning, so an object file compiled against the reference header links
+ * against this library unchanged.  Every entry point is also exported with C linkage (plain pointers and
+ * sizes, `int` carrying a cudaError_t) for FFI callers; those are the symbols a ctypes / cgo / JNI binding
+ * would bind.  Matrix layouts are the reference's:
+ *     A  row-major [M][K] fp16 (weights; only its tiled-CSL encoding is read by the kernel)
+ *     B  row-major [N][K] fp16 ("column-major K x N": tokens x hidden)
+ *     C  row-major [N][M] fp16 ("column-major M x N")
+ *     C[n][m] = sum_k A[m][k] * B[n][k], fp32 accumulation, one fp16 rounding at the end.
+ *
+ * Tiled-CSL: A is cut into 128x64 tiles, tile id t = (m/128)*(K/64) + k/64.  Each nonzero is one 32-bit word,
+ * low half = fp16 bits, high half = r*64 + (c ^ ((r & 7) << 3)) for the in-tile cell (r, c).  A tile's words
+ * are padded with zero-valued words to a multiple of four.  TileOffsets[t] counts 16-byte vectors before tile
+ * t; it has T+2 entries and the last two are equal.
+ */
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Reference-compatible C++ entry points
+ * ---------------------------------------------------------------------------------------------------------- */
+
+/* Replaces SpMM_SplitK_API (reference build/SpMM_API.cuh:38-48, csrc/SpMM_API.cu:55-130).
+ * All pointers are device pointers.  `A` is never read (callers pass nullptr).  Enqueues on `stream` and
+ * returns without synchronising.  N must be 8, 16, 32, 64 or a multiple of 128 (otherwise the reference's
+ * message is printed and cudaErrorUnknown returned); M % 128 == 0 and K % 64 == 0 (the reference kernel needs
+ * M % 256 == 0 for N <= 32; this one does not).  Split_K >= 1 is a hint: the kernel always splits K inside
+ * thread-block clusters and sums the parts in fp32 through distributed shared memory, and additionally uses up
+ * to Split_K fp16 partial matrices in Reduction_Workspace (>= Split_K*M*N halves, may be nullptr when
+ * Split_K == 1) when that fills the GPU better. */
+cudaError_t SpMM_SplitK_API(cudaStream_t stream,
+                            const half*  A,
+                            const uint4* Compressed_A,
+                            const int*   TileOffsets,
+                            const half*  B,
+                            half*        C,
+                            const int    M_Global,
+                            const int    N_Global,
+                            const int    K_Global,
+                            half*        Reduction_Workspace,
+                            int          Split_K);
+
+/* Replaces InitSparseMatrixA_API (reference build/SpMM_API.cuh:51, csrc/SpMM_API.cu:163-360).
+ * Host encoder, dense fp16 -> tiled-CSL with the bank-aware in-tile ordering.  Output is bit-identical to the
+ * reference's.  Both outputs are malloc'ed; the caller frees them with free().  `N` is ignored.  Returns the
+ * number of TileOffsets entries, (M/128)*(K/64) + 2.  Prints and exits on allocation failure, as the
+ * reference does. */
+__host__ int InitSparseMatrixA_API(half* A_h, int M, int N, int K, uint32_t** Compressed_A, int** TileOffsets);
+
+/* Replaces InitSparseMatrixA_API_NoReorder (reference build/SpMM_API.cuh:53-58, csrc/SpMM_API.cu:363-489):
+ * same format, words in row-major scan order. */
+__host__ int
+InitSparseMatrixA_API_NoReorder(half* A_h, int M, int N, int K, uint32_t** Compressed_A, int** TileOffsets);
+
+extern "C" {
+
+/* Replaces GenSparseMatrixBinFile (definition at reference csrc/SpMM_API.cu:500-555, called through ctypes with
+ * these six arguments by end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:52-59; the reference
+ * header's seven-argument prototype does not match its own definition).  Reads M*K fp16 from the dense file and
+ * writes {NNZ, NumOffsets} as two int32, NNZ uint32 words, and NumOffsets int32 offsets. */
+void GenSparseMatrixBinFile(char* DenseMatrixFileName,
+                            int   M,
+                            int   K,
+                            char* NZWeightsFileName,
+                            char* TileOffsetsFileName,
+                            char* OutputSizesFileName);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * C-ABI aliases (FFI).  `int` results are cudaError_t values unless stated otherwise.
+ * ---------------------------------------------------------------------------------------------------------- */
+
+/* C-linkage form of SpMM_SplitK_API (reference csrc/SpMM_API.cu:55). `stream` is a cudaStream_t. */
+int FlashLLM_SpMM_SplitK(void*       stream,
+                         const void* A,
+                         const void* Compressed_A,
+                         const int*  TileOffsets,
+                         const void* B,
+                         void*       C,
+                         int         M,
+                         int         N,
+                         int         K,
+                         void*       Reduction_Workspace,
+                         int         Split_K);
+
+/* C-linkage forms of the host encoders (reference csrc/SpMM_API.cu:163 and :363); return NumOffsets. */
+int FlashLLM_InitSparseMatrixA(const void* A_h, int M, int N, int K, uint32_t** Compressed_A, int** TileOffsets);
+int FlashLLM_InitSparseMatrixA_NoReorder(const void* A_h, int M, int N, int K, uint32_t** Compressed_A,
+                                         int** TileOffsets);
+/* free() for buffers returned by the two encoders above, for callers without access to the C allocator. */
+void FlashLLM_Free(void* p);
+
+/* Device encoder, step 1 (device-side counterpart of the counting passes, reference csrc/SpMM_API.cu:200-216):
+ * fills TileOffsets_d[0 .. T+1] (T+2 ints) from the dense row-major fp16 device matrix A_d.  Stream-ordered, no
+ * scratch memory; bit-identical to the host encoder's TileOffsets. */
+int FlashLLM_EncodeOnDevice_TileOffsets(void* stream, const void* A_d, int M, int K, int* TileOffsets_d);
+
+/* Device encoder, step 2 (device-side counterpart of reference csrc/SpMM_API.cu:236-350): writes the packed
+ * words, bit-identical to InitSparseMatrixA_API (reorder != 0) or InitSparseMatrixA_API_NoReorder (reorder == 0).
+ * Compressed_A_d must hold 4*TileOffsets[T+1] words (read TileOffsets_d[T+1] back after step 1 to size it). */
+int FlashLLM_EncodeOnDevice_Pack(void* stream, const void* A_d, int M, int K, const int* TileOffsets_d,
+                                 uint32_t* Compressed_A_d, int reorder);
+
+/* Split-K reduction on its own (reference csrc/Reduction_Kernel.cuh:24-45):
+ * C[i] = fp16(sum_s float(Workspace[s*M*N + i])). */
+int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K);
+
+/* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
+ * csrc/SpMM_API.cu:79-118): fixes the launch plan for subsequent calls from this process; 0 = choose
+ * automatically.  cluster_k: K parts summed inside a cluster (1..8); workspace_k: extra K parts through
+ * Reduction_Workspace (capped by the caller's Split_K); a_stages / b_stages: dense-tile and B-tile pipeline
+ * depth; ring_slots x chunk_vectors(16 B each): compressed-stream ring; scatter_warps: 4 or 8. */
+void FlashLLM_SetPlan(int cluster_k, int workspace_k, int a_stages, int b_stages, int ring_slots, int chunk_vectors,
+                      int scatter_warps);
+
+/* Describes the plan the next SpMM call with these sizes would use; fills out[0..7] =
+ * {cluster_k, workspace_k, a_stages, b_stages, ring_slots, chunk_vectors, scatter_warps, dynamic smem bytes}. */
+int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out);
+
+/* Reads and clears the device-side status word of the current device (synchronises the device).  0 = no kernel of
+ * this library gave up on a bounded wait or met a malformed TileOffsets since the last call. */
+unsigned int FlashLLM_ConsumeStatus(void);
+
+/* Number of kernels this library has launched from this process (all devices). */
+unsigned long long FlashLLM_LaunchCount(void);
+
+}  // extern "C"
