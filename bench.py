@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the SpMM hot path: effective TFLOP/s of the OPT-66B-shaped skinny SpMMs at N = 16, 80 % sparsity.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference-gpu]
+
+One step = the four sparse matmuls of one OPT-66B decoder layer (QKV 27648x9216, out-proj 9216x9216,
+FFN1 36864x9216, FFN2 9216x36864) on N = 16 tokens, fp16, weights 80 % unstructured-sparse in tiled-CSL.
+With --gpus N > 1 (one process per GPU, launched by torch.distributed.run) the weight rows (output features) of
+every matrix are partitioned evenly over the ranks; there is no data-path collective, the job-wide time is the
+maximum over ranks.  Inputs are seeded synthetic matrices of those shapes (no checkpoint is read).
+
+Prints one JSON line: metric/value/unit (whole-job effective TFLOP/s = 2*M*N*K summed over the four matmuls and
+the steps, divided by the device time), `e2e` (the same through the C ABI with HOST activations and results:
+pinned H2D copy of B and D2H copy of C inside the timed region), `roofline` of the dominant kernel (FFN1-shaped
+SpMM, algorithmic bytes / CUDA-event time against the measured HBM copy bandwidth) and `cpu_baseline` (host fp32
+dense GEMM of the oracle on a bounded row sample, all host threads).
+
+--impl reference        times that CPU path alone (reference host encoder + host dense GEMM), rank 0 only.
+--impl reference-gpu    times the unmodified reference CUDA kernel (built from its own sources) on the same inputs.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+# (name, M, K, reference's hand-tuned Split_K for the shape: kernel_benchmark/benchmark.sh:13-15)
+OPT66B_LAYER = [("qkv", 27648, 9216, 2), ("out_proj", 9216, 9216, 6), ("ffn1", 36864, 9216, 3), ("ffn2", 9216, 36864, 6)]
+N_TOKENS = 16
+SPARSITY = 0.8
+SEED = 0xF1A50000
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons for one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            self.proc.wait()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [v for v in vis.split(",") if v.strip()]
+        if local_rank < len(ids) and ids[local_rank].strip().isdigit():
+            return int(ids[local_rank])
+    return local_rank
+
+
+class Layer:
+    """One rank's row shard of the four weight matrices, encoded on the device, plus activations and outputs."""
+
+    def __init__(self, fl, rank: int, world: int, dev):
+        self.fl, self.dev, self.items = fl, dev, []
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        for idx, (name, M, K, split_k) in enumerate(OPT66B_LAYER):
+            assert M % (128 * world) == 0, (name, M, world)
+            rows = (rank * M // world, (rank + 1) * M // world)
+            m = rows[1] - rows[0]
+            A = fl.synthetic.sparse_uniform_matrix(M, K, SPARSITY, SEED + idx, device=dev, rows=rows)
+            comp, offs, num_offsets, words = fl.encode_on_device(
+                stream, A.data_ptr(), m, K,
+                lambda n: (lambda t: (t, t.data_ptr()))(torch.empty(n, dtype=torch.int32, device=dev)),
+                lambda n: (lambda t: (t, t.data_ptr()))(torch.empty(n, dtype=torch.int32, device=dev)),
+                lambda owner, i: owner[i].item())
+            del A
+            B = fl.synthetic.dense_uniform_matrix(N_TOKENS, K, (SEED + idx) ^ 0xB, device=dev)
+            item = dict(name=name, M_full=M, M=m, K=K, split_k=split_k, comp=comp, offs=offs, words=words, B=B,
+                        C=torch.empty((N_TOKENS, m), dtype=torch.float16, device=dev),
+                        ws=torch.empty((split_k, N_TOKENS, m), dtype=torch.float16, device=dev),
+                        B_host=B.cpu().pin_memory(),
+                        C_host=torch.empty((N_TOKENS, m), dtype=torch.float16).pin_memory(),
+                        bytes_alg=4 * words + 4 * num_offsets + 2 * K * N_TOKENS + 2 * m * N_TOKENS)
+            self.items.append(item)
+        torch.cuda.synchronize(dev)
+
+    def spmm(self, it, stream):
+        self.fl.SpMM_SplitK_API(stream, None, it["comp"].data_ptr(), it["offs"].data_ptr(), it["B"].data_ptr(),
+                                it["C"].data_ptr(), it["M"], N_TOKENS, it["K"], it["ws"].data_ptr(), it["split_k"])
+
+    def step(self, stream):
+        for it in self.items:
+            self.spmm(it, stream)
+
+    def step_e2e(self, stream):
+        for it in self.items:
+            it["B"].copy_(it["B_host"], non_blocking=True)
+            self.spmm(it, stream)
+            it["C_host"].copy_(it["C"], non_blocking=True)
+
+
+def time_loop(fn, steps: int, dev) -> float:
+    """Milliseconds for `steps` calls of fn, CUDA events on the current stream, synchronised on both sides."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize(dev)
+    return start.elapsed_time(stop)
+
+
+def cpu_baseline(sample_seconds: float = 12.0) -> dict:
+    """Host fp32 dense GEMM (OpenMP, all host threads) on a row sample of the FFN1-shaped matrix."""
+    import flash_llm_b200 as fl
+    from oracle import cpu_oracle
+    name, M, K, _ = OPT66B_LAYER[2]
+    cores = os.cpu_count() or 1
+    rows = 1024
+    A = fl.synthetic.sparse_uniform_matrix(M, K, SPARSITY, SEED + 2, rows=(0, rows)).numpy()
+    B = fl.synthetic.dense_uniform_matrix(N_TOKENS, K, (SEED + 2) ^ 0xB).numpy()
+    cpu_oracle.gemm_f32(A[:128], B, timed=True)  # warm the thread pool
+    t0, reps = time.perf_counter(), 0
+    while True:
+        cpu_oracle.gemm_f32(A, B, timed=True)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > sample_seconds or reps >= 200:
+            break
+    tflops = 2.0 * rows * N_TOKENS * K * reps / dt / 1e12
+    t0 = time.perf_counter()
+    if cpu_oracle.reference_available():
+        cpu_oracle.reference_encode(A, True)
+        enc_kind = "reference"
+    else:
+        cpu_oracle.encode(A, True)
+        enc_kind = "port"
+    enc_s = time.perf_counter() - t0
+    return {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{reps} x host fp32 dense GEMM of {rows} of the {M} rows of the {name} matrix ({M}x{K}, N={N_TOKENS}); "
+                      f"single-thread {enc_kind} tiled-CSL encode of those rows took {enc_s:.2f} s "
+                      f"(~{enc_s * M / rows:.0f} s for the matrix)"}
+
+
+def config_dict(world: int) -> dict:
+    return {"workload": "OPT-66B decoder-layer SpMMs (27648x9216, 9216x9216, 36864x9216, 9216x36864), N=16 tokens, "
+                        "80% uniform-random sparsity, fp16, tiled-CSL, Split_K hints 2/6/3/6",
+            "sharding": f"weight rows split evenly over {world} GPU(s), no collective",
+            "l2": "inputs larger than L2: each step streams ~821 MB of compressed weights (126 MB L2)",
+            "tokens": N_TOKENS, "sparsity": SPARSITY}
+
+
+def run_ours(args) -> None:
+    import flash_llm_b200 as fl
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    fl.library()
+    layer = Layer(fl, rank, world, dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput
+    for _ in range(max(args.warmup, 3)):
+        layer.step(stream)
+    barrier()
+    launches_before = fl.launch_count()
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        ms = time_loop(lambda: layer.step(stream), args.steps, dev)
+    launches = fl.launch_count() - launches_before
+    barrier()
+    ms = max_over_ranks(ms)
+    status = fl.consume_status()
+    assert status == 0, f"kernel status {status:#x}"
+    flops_per_step = sum(2.0 * M * N_TOKENS * K for _, M, K, _ in OPT66B_LAYER)
+    value = flops_per_step * args.steps / (ms * 1e-3) / 1e12
+
+    # ---- end to end: host activations in, host results out, every step
+    for _ in range(3):
+        layer.step_e2e(stream)
+    barrier()
+    ms_e2e = max_over_ranks(time_loop(lambda: layer.step_e2e(stream), args.steps, dev))
+    barrier()
+    h2d = sum(it["B_host"].numel() * 2 for it in layer.items)
+    d2h = sum(it["C_host"].numel() * 2 for it in layer.items)
+    e2e_value = flops_per_step * args.steps / (ms_e2e * 1e-3) / 1e12
+
+    # ---- per-kernel numbers (rank 0): every shape alone, dominant one for the roofline
+    per_shape = {}
+    for it in layer.items:
+        for _ in range(5):
+            layer.spmm(it, stream)
+        reps = max(20, args.steps)
+        t = time_loop(lambda it=it: layer.spmm(it, stream), reps, dev) / reps
+        per_shape[it["name"]] = {"ms": t, "gbs": it["bytes_alg"] / (t * 1e-3) / 1e9,
+                                 "tflops": 2.0 * it["M"] * N_TOKENS * it["K"] / (t * 1e-3) / 1e12,
+                                 "bytes_alg": it["bytes_alg"],
+                                 "plan": fl.get_plan(it["M"], N_TOKENS, it["K"], it["split_k"])}
+    peak, peak_kind = measured_peak_gbs()
+    dom = per_shape["ffn1"]
+    roofline = {"bound": "hbm", "kernel": "spmm_tcgen05_kernel<16> on the FFN1 shard", "achieved": dom["gbs"],
+                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": dom["gbs"] / peak,
+                "frac_of_nominal_8000": dom["gbs"] / 8000.0, "traffic": None, "launch_ms": dom["ms"],
+                "algorithmic_bytes": dom["bytes_alg"]}
+
+    if rank == 0:
+        line = {"metric": "spmm_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+                "data": "synthetic", "config": config_dict(world),
+                "hbm_gbs": sum(it["bytes_alg"] for it in layer.items) * args.steps / (ms * 1e-3) / 1e9,
+                "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": ms_e2e / args.steps},
+                "gpu_launches": launches, "clocks": clocks.summary(), "roofline": roofline, "per_shape": per_shape}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference_cpu(args) -> None:
+    """The reference's CPU path for this operation: host tiled-CSL encode + host fp32 dense GEMM."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    steps = max(args.steps, 1)
+    # one step = a bounded row sample of the workload, sized for a few seconds of host time
+    per_step = max(2.0, min(20.0, 90.0 / (steps + max(args.warmup, 0))))
+    for _ in range(min(args.warmup, 1)):
+        cpu_baseline(1.0)
+    t0 = time.perf_counter()
+    results = [cpu_baseline(per_step) for _ in range(steps)]
+    wall = time.perf_counter() - t0
+    value = statistics.mean(r["value"] for r in results)
+    base = results[-1]
+    base["value"] = value
+    line = {"impl": "reference", "metric": "spmm_effective_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": wall * 1e3 / steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_dict(args.gpus), "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu(args) -> None:
+    """The unmodified reference CUDA kernel (compiled for sm_100a from its own sources) on the same inputs."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import flash_llm_b200 as fl
+    from oracle import cpu_oracle
+    if not cpu_oracle.reference_available():
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref/libSpMM_API_ref.so has not been built"}))
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    layer = Layer(fl, 0, 1, dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def step():
+        for it in layer.items:
+            rc = cpu_oracle.reference_spmm(stream, it["comp"].data_ptr(), it["offs"].data_ptr(), it["B"].data_ptr(),
+                                           it["C"].data_ptr(), it["M"], N_TOKENS, it["K"], it["ws"].data_ptr(), it["split_k"])
+            assert rc == 0, rc
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ms = time_loop(step, args.steps, dev)
+    flops_per_step = sum(2.0 * M * N_TOKENS * K for _, M, K, _ in OPT66B_LAYER)
+    per_shape = {}
+    for it in layer.items:
+        def one(it=it):
+            cpu_oracle.reference_spmm(stream, it["comp"].data_ptr(), it["offs"].data_ptr(), it["B"].data_ptr(),
+                                      it["C"].data_ptr(), it["M"], N_TOKENS, it["K"], it["ws"].data_ptr(), it["split_k"])
+        t = time_loop(one, 20, dev) / 20
+        per_shape[it["name"]] = {"ms": t, "gbs": it["bytes_alg"] / (t * 1e-3) / 1e9}
+    print(json.dumps({"impl": "reference-gpu", "metric": "spmm_effective_tflops",
+                      "value": flops_per_step * args.steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+                      "higher_is_better": True, "dtype": "f16", "data": "synthetic", "config": config_dict(1),
+                      "per_shape": per_shape}), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_cpu(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

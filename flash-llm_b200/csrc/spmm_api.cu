@@ -165,14 +165,14 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     if (pl.cluster_k > k_tiles)
         pl.cluster_k = k_tiles;
     int extra = ov.workspace_k ? ov.workspace_k : (want + pl.cluster_k - 1) / pl.cluster_k;
-    if (extra > Split_K)
-        extra = Split_K;  // the workspace is only promised to hold Split_K partial matrices
+    if (extra > Split_K / 2)
+        extra = Split_K / 2;  // the workspace is promised to hold Split_K fp16 matrices = Split_K/2 fp32 partials
     if (extra * pl.cluster_k > k_tiles)
         extra = k_tiles / pl.cluster_k;
     if (extra < 1)
         extra = 1;
-    if ((static_cast<long long>(M) * N) % 8 != 0)
-        extra = 1;  // the workspace reduction moves eight halves per thread
+    if ((static_cast<long long>(M) * N) % 4 != 0)
+        extra = 1;  // the workspace reduction moves four values per thread
     pl.workspace_k = extra;
     pl.smem_bytes  = plan_smem_bytes(pl);
 
@@ -209,6 +209,16 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cfg.numAttrs             = 1;
     count_launch();
     return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
+}
+
+static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws, long long count, int parts)
+{
+    const int       threads = 256;
+    const long long groups  = (count + 3) / 4;
+    const unsigned  blocks  = static_cast<unsigned>((groups + threads - 1) / threads);
+    count_launch();
+    splitk_reduce_f32_kernel<<<blocks, threads, 0, stream>>>(C, ws, count, parts);
+    return cudaGetLastError();
 }
 
 static cudaError_t reduce_workspace(cudaStream_t stream, half* C, const half* ws, long long count, int parts)
@@ -265,14 +275,15 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     if ((err = make_plan(st, M_Global, N_Global, K_Global, Split_K, &params.plan)) != cudaSuccess)
         return err;
     SpmmPlan& pl = params.plan;
-    // A partial-matrix pass needs 16-byte aligned rows of eight halves in both buffers.
+    // The partial-matrix pass reads 16-byte groups of the workspace and writes 8-byte groups of C.
     if (pl.workspace_k > 1
-        && ((reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u) != 0 || (reinterpret_cast<uintptr_t>(C) & 15u) != 0))
+        && ((reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u) != 0 || (reinterpret_cast<uintptr_t>(C) & 7u) != 0))
         pl.workspace_k = 1;
 
     params.compressed   = Compressed_A;
     params.tile_offsets = TileOffsets;
-    params.out          = pl.workspace_k > 1 ? Reduction_Workspace : C;
+    params.out          = C;
+    params.partial      = pl.workspace_k > 1 ? reinterpret_cast<float*>(Reduction_Workspace) : nullptr;
     params.status       = st->status;
     params.M            = M_Global;
     params.N            = N_Global;
@@ -302,8 +313,7 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     if (err != cudaSuccess)
         return err;
     if (pl.workspace_k > 1)
-        return reduce_workspace(stream, C, Reduction_Workspace, static_cast<long long>(M_Global) * N_Global,
-                                pl.workspace_k);
+        return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k);
     return cudaSuccess;
 }
 

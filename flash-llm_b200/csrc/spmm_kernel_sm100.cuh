@@ -29,7 +29,8 @@ namespace flashllm {
 struct SpmmParams {
     const uint4*  compressed;    // tiled-CSL words viewed as 16-byte vectors
     const int*    tile_offsets;  // T + 2 prefix sums, in vectors
-    half*         out;           // C, or the fp16 partial matrices when workspace_k > 1
+    half*         out;           // C (used when workspace_k == 1)
+    float*        partial;       // workspace_k fp32 partial matrices [N][M] (used when workspace_k > 1)
     unsigned int* status;        // per-device status word
     int           M, N, K;
     int           k_tiles;  // K / 64
@@ -395,8 +396,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         const int col_end       = (col_begin + col_share) < N_TILE ? (col_begin + col_share) : N_TILE;
         const int n_valid       = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
         const int row_in_tile   = quarter * 32 + lane;
-        half* const out_part    = p.out + (G > 1 ? static_cast<size_t>(g) * p.M * p.N : 0);
-        half* const out_tile    = out_part + static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
+        const size_t tile_off   = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
+        half* const  out_tile   = p.out + tile_off;
+        float* const part_tile  = G > 1 ? p.partial + static_cast<size_t>(g) * p.M * p.N + tile_off : nullptr;
         float* const red        = reinterpret_cast<float*>(smem);  // [N_TILE][128] fp32, over the idle A stages
 
         for (int c0 = col_begin; c0 < col_end; c0 += 8) {
@@ -414,9 +416,13 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                 if (acc_ok) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        if (c0 + i < n_valid)
-                            out_tile[static_cast<size_t>(c0 + i) * p.M + row_in_tile] =
-                                __float2half_rn(__uint_as_float(r[i]));
+                        if (c0 + i < n_valid) {
+                            const size_t at = static_cast<size_t>(c0 + i) * p.M + row_in_tile;
+                            if (part_tile)
+                                part_tile[at] = __uint_as_float(r[i]);
+                            else
+                                out_tile[at] = __float2half_rn(__uint_as_float(r[i]));
+                        }
                 }
             }
             else {
@@ -440,8 +446,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
             const int      lo       = static_cast<int>(static_cast<long long>(total) * rank / S);
             const int      hi       = static_cast<int>(static_cast<long long>(total) * (rank + 1) / S);
             const bool     store_ok = (*abort_flag == 0u);
-            half* const    out_part = p.out + (G > 1 ? static_cast<size_t>(g) * p.M * p.N : 0);
-            half* const    out_tile = out_part + static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
+            const size_t   tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
+            half* const    out_tile = p.out + tile_off;
+            float* const   part_tile = G > 1 ? p.partial + static_cast<size_t>(g) * p.M * p.N + tile_off : nullptr;
             for (int e = lo + tid_s; e < hi; e += NTS) {
                 const int n = e / kTileM, m = e % kTileM;
                 if (n >= n_valid)
@@ -449,8 +456,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                 float acc = 0.0f;
                 for (int q = 0; q < S; ++q)
                     acc += ptx::ld_dsmem_f32(ptx::map_to_rank(base + static_cast<uint32_t>(e) * 4u, q));
-                if (store_ok)
-                    out_tile[static_cast<size_t>(n) * p.M + m] = __float2half_rn(acc);
+                if (store_ok) {
+                    if (part_tile)
+                        part_tile[static_cast<size_t>(n) * p.M + m] = acc;
+                    else
+                        out_tile[static_cast<size_t>(n) * p.M + m] = __float2half_rn(acc);
+                }
             }
         }
         __syncwarp();
@@ -462,8 +473,30 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     }
 }
 
-// Sums the fp16 partial matrices of the workspace path (reference csrc/Reduction_Kernel.cuh:24-45):
-// C[i] = fp16(sum_s float(ws[s*count + i])); eight outputs per thread, 16-byte accesses.
+// Sums the fp32 partial matrices this library parks in the caller's workspace when workspace_k > 1 and rounds once:
+// C[i] = fp16(sum_s ws[s*count + i]); four outputs per thread.
+__global__ void splitk_reduce_f32_kernel(half* __restrict__ C, const float* __restrict__ ws, long long count, int parts)
+{
+    const long long i4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i4 >= count)
+        return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < parts; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(ws + static_cast<long long>(s) * count + i4);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+    }
+    uint2    o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+    oh[0]       = __floats2half2_rn(acc.x, acc.y);
+    oh[1]       = __floats2half2_rn(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(C + i4) = o;
+}
+
+// The reference's reduction semantics, kept as an entry point of its own (reference csrc/Reduction_Kernel.cuh:24-45):
+// C[i] = fp16(sum_s float(ws[s*count + i])) over fp16 partial matrices; eight outputs per thread, 16-byte accesses.
 __global__ void splitk_reduce_kernel(half* __restrict__ C, const half* __restrict__ ws, long long count, int parts)
 {
     const long long i8 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;

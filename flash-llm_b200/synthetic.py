@@ -36,17 +36,20 @@ def uniform01(seed: int, start: int, count: int, device, stream_id: int = 0) -> 
     return _lsr(z, 40).to(torch.float32) * (1.0 / (1 << 24))
 
 
-def sparse_uniform_matrix(M: int, K: int, sparsity: float, seed: int, device="cpu", rows_per_block: int = 2048):
-    """fp16 ``[M][K]``: Bernoulli(1 - sparsity) mask, non-zeros U(-1, 1) (never rounding to zero)."""
-    out = torch.empty((M, K), dtype=torch.float16, device=device)
-    for r0 in range(0, M, rows_per_block):
-        r1 = min(M, r0 + rows_per_block)
+def sparse_uniform_matrix(M: int, K: int, sparsity: float, seed: int, device="cpu", rows_per_block: int = 2048,
+                          rows: tuple[int, int] | None = None):
+    """fp16 ``[M][K]``: Bernoulli(1 - sparsity) mask, non-zeros U(-1, 1) (never rounding to zero).
+    ``rows=(r0, r1)`` returns only that row range of the same matrix (a row shard)."""
+    lo, hi = rows if rows is not None else (0, M)
+    out = torch.empty((hi - lo, K), dtype=torch.float16, device=device)
+    for r0 in range(lo, hi, rows_per_block):
+        r1 = min(hi, r0 + rows_per_block)
         n = (r1 - r0) * K
         keep = uniform01(seed, r0 * K, n, device, 0) >= sparsity
         val = uniform01(seed, r0 * K, n, device, 1) * 2.0 - 1.0
         tiny = val.abs() < 6.2e-5
         val = torch.where(tiny, torch.where(val < 0, -6.2e-5, 6.2e-5).to(val.dtype), val)
-        out[r0:r1] = torch.where(keep, val, torch.zeros_like(val)).to(torch.float16).view(r1 - r0, K)
+        out[r0 - lo:r1 - lo] = torch.where(keep, val, torch.zeros_like(val)).to(torch.float16).view(r1 - r0, K)
     return out
 
 

@@ -30,9 +30,9 @@
  * returns without synchronising.  N must be 8, 16, 32, 64 or a multiple of 128 (otherwise the reference's
  * message is printed and cudaErrorUnknown returned); M % 128 == 0 and K % 64 == 0 (the reference kernel needs
  * M % 256 == 0 for N <= 32; this one does not).  Split_K >= 1 is a hint: the kernel always splits K inside
- * thread-block clusters and sums the parts in fp32 through distributed shared memory, and additionally uses up
- * to Split_K fp16 partial matrices in Reduction_Workspace (>= Split_K*M*N halves, may be nullptr when
- * Split_K == 1) when that fills the GPU better. */
+ * thread-block clusters and sums the parts in fp32 through distributed shared memory; when that alone does not
+ * fill the GPU it also parks up to Split_K/2 fp32 partial matrices in Reduction_Workspace (>= Split_K*M*N halves,
+ * 16-byte aligned; may be nullptr when Split_K == 1) and rounds to fp16 once, after summing them. */
 cudaError_t SpMM_SplitK_API(cudaStream_t stream,
                             const half*  A,
                             const uint4* Compressed_A,
@@ -112,7 +112,7 @@ int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Works
 /* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
  * csrc/SpMM_API.cu:79-118): fixes the launch plan for subsequent calls from this process; 0 = choose
  * automatically.  cluster_k: K parts summed inside a cluster (1..8); workspace_k: extra K parts through
- * Reduction_Workspace (capped by the caller's Split_K); a_stages / b_stages: dense-tile and B-tile pipeline
+ * Reduction_Workspace (capped at Split_K/2 of the call, as each fp32 partial matrix takes two fp16 ones' room); a_stages / b_stages: dense-tile and B-tile pipeline
  * depth; ring_slots x chunk_vectors(16 B each): compressed-stream ring; scatter_warps: 4 or 8. */
 void FlashLLM_SetPlan(int cluster_k, int workspace_k, int a_stages, int b_stages, int ring_slots, int chunk_vectors,
                       int scatter_warps);
