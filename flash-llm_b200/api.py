@@ -14,7 +14,8 @@ import numpy as np
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_PKG)
-LIBRARY_PATH = os.path.join(_ROOT, "build", "libSpMM_API.so")
+# FLASHLLM_LIBRARY selects another build of the same library (e.g. a pipeline-analysis build).
+LIBRARY_PATH = os.environ.get("FLASHLLM_LIBRARY") or os.path.join(_ROOT, "build", "libSpMM_API.so")
 
 _u32p = C.POINTER(C.c_uint32)
 _i32p = C.POINTER(C.c_int)

@@ -121,7 +121,7 @@ static int n_tile_for(int N)
 
 static int plan_smem_bytes(const SpmmPlan& pl)
 {
-    const int bars = 8 * (2 * pl.ring_slots + 2 * pl.a_stages + 2 * pl.b_stages + 1) + 16;
+    const int bars = 8 * (2 * pl.ring_slots + 2 * pl.a_stages + 2 * pl.b_stages + 1) + 16 + 4 * pl.offsets_staged;
     return 1024 /* alignment slack */ + pl.a_stages * kDenseTileBytes + pl.b_stages * pl.n_tile * kTileK * 2
            + pl.ring_slots * pl.chunk_vectors * 16 + bars;
 }
@@ -174,7 +174,10 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     if ((static_cast<long long>(M) * N) % 4 != 0)
         extra = 1;  // the workspace reduction moves four values per thread
     pl.workspace_k = extra;
-    pl.smem_bytes  = plan_smem_bytes(pl);
+    // room for this CTA's slice of TileOffsets (K tiles of the longest part, plus one), up to 8 KB
+    const int longest = (k_tiles + pl.cluster_k * pl.workspace_k - 1) / (pl.cluster_k * pl.workspace_k) + 1;
+    pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
+    pl.smem_bytes     = plan_smem_bytes(pl);
 
     const bool ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8) && is_pow2(pl.chunk_vectors)
                     && pl.chunk_vectors >= 64 && pl.ring_slots <= kMaxRingSlots
@@ -183,7 +186,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
                     && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK && pl.workspace_k >= 1
                     && pl.smem_bytes <= st->smem_optin
                     // the fp32 partial tile of the cluster reduction is parked over the pipeline buffers
-                    && pl.smem_bytes - 2048 >= pl.n_tile * kTileM * 4;
+                    && pl.smem_bytes - 2048 - 4 * pl.offsets_staged >= pl.n_tile * kTileM * 4;
     if (!ok)
         return cudaErrorInvalidConfiguration;
     *out = pl;

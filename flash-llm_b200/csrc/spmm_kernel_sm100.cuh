@@ -39,6 +39,13 @@ struct SpmmParams {
 
 constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
 
+// Pipeline-analysis builds (never the shipped one) drop one stage of the kernel to see what it costs, as the
+// reference does with its own stubs (csrc/SpMM_Kernel.cuh:64-111).  Bits: 1 no zero-fill, 2 no scatter stores,
+// 4 no MMA, 8 no ring reads, 16 no scatter-warp barrier.  Results are wrong with any bit set.
+#ifndef FLASHLLM_ABLATE
+#define FLASHLLM_ABLATE 0
+#endif
+
 // Spins on one mbarrier phase.  Returns false when the CTA has been told to give up, or after kWaitLimitNs,
 // in which case it raises the abort flag and the status bit itself.
 __device__ __forceinline__ bool
@@ -147,6 +154,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     const uint32_t misc_off   = (acc_full + 8u) - base;
     volatile uint32_t* const tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem + misc_off);
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(smem + misc_off + 4);
+    int* const               offs_stage = reinterpret_cast<int*>(smem + misc_off + 16);  // plan.offsets_staged ints
 
     // ---- work assignment: blockIdx.x = K part inside the cluster, y = tile row, z = (N tile, workspace part)
     const int rank     = blockIdx.x;
@@ -207,7 +215,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
             uint64_t     t0    = 0;
             while (c < nchunks || j < L) {
                 bool progressed = false;
-                if (c < nchunks && ptx::mbar_try_wait(ring_empty + 8u * c_slot, (c_use & 1u) ^ 1u)) {
+                if (c < nchunks && ptx::mbar_test_wait(ring_empty + 8u * c_slot, (c_use & 1u) ^ 1u)) {
                     const int      left  = nvec - c * CV;
                     const uint32_t bytes = static_cast<uint32_t>(left < CV ? left : CV) * 16u;
                     const uint32_t bar   = ring_full + 8u * c_slot;
@@ -221,7 +229,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                     }
                     progressed = true;
                 }
-                if (j < L && ptx::mbar_try_wait(b_empty + 8u * j_slot, (j_use & 1u) ^ 1u)) {
+                if (j < L && ptx::mbar_test_wait(b_empty + 8u * j_slot, (j_use & 1u) ^ 1u)) {
                     const uint32_t bar = b_full + 8u * j_slot;
                     ptx::mbar_arrive_expect_tx(bar, kBBytes);
                     ptx::tma_load_2d(b_base + j_slot * kBBytes, &tmap_b, (k_begin + j) * kTileK, n_idx * N_TILE, bar);
@@ -235,11 +243,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                 if (progressed) {
                     idle = 0;
                 }
-                else if ((++idle & 63u) == 0u) {
+                else if ((++idle & 1023u) == 0u) {
                     if (*abort_flag)
                         break;
                     const uint64_t now = ptx::globaltimer_ns();
-                    if (idle == 64u)
+                    if (idle == 1024u)
                         t0 = now;
                     else if (now - t0 > kWaitLimitNs) {
                         *abort_flag = 1u;
@@ -281,7 +289,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                 const uint32_t a_addr = a_base + s * kDenseTileBytes;
                 const uint32_t b_addr = b_base + bs * kBBytes;
 #pragma unroll
-                for (int kk = 0; kk < kTileK / kUmmaK; ++kk) {
+                for (int kk = 0; kk < ((FLASHLLM_ABLATE & 4) ? 0 : kTileK / kUmmaK); ++kk) {
                     ptx::umma_f16_ss(tmem_acc,
                                      ptx::umma_desc_kmajor_sw128(a_addr + kk * kUmmaK * 2),
                                      ptx::umma_desc_kmajor_sw128(b_addr + kk * kUmmaK * 2),
@@ -306,8 +314,16 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         // ================================================================ scatter warps
         const int tid_s = threadIdx.x - kControlWarps * 32;
         if (L > 0) {
-            const int v_first  = offs[0];
-            int       next_off = offs[1];
+            // This CTA's slice of TileOffsets is read once, together, instead of one dependent load per tile.
+            const int* offs_local = offs;
+            if (L + 1 <= plan.offsets_staged) {
+                for (int i = tid_s; i <= L; i += NTS)
+                    offs_stage[i] = offs[i];
+                ptx::named_barrier_sync(1, NTS);
+                offs_local = offs_stage;
+            }
+            const int v_first  = offs_local[0];
+            int       next_off = offs_local[1];
             int       vb       = 0;  // first vector of the current tile, relative to v_first
             int       ready    = 0;  // ring chunks known to have landed
             int       ready_slot = 0;
@@ -320,7 +336,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
             for (int j = 0; j < L; ++j) {
                 const int ve = next_off - v_first;
                 if (j + 1 < L)
-                    next_off = offs[j + 2];
+                    next_off = offs_local[j + 2];
                 bool bad = (ve < vb) || (ve - vb > kMaxTileVectors);
                 if (bad)
                     atomicOr(p.status, kStatusBadTileOffsets);
@@ -340,28 +356,40 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                         }
                     }
                 }
-                if (ok) {
+                if (ok && !(FLASHLLM_ABLATE & 1)) {
                     for (uint32_t off = tid_s * 16u; off < kDenseTileBytes; off += NTS * 16u)
                         sts_zero16(stage + off);
                 }
                 // Zeroes must be in place before any warp scatters; the same barrier makes giving up unanimous.
+#if (FLASHLLM_ABLATE & 16)
+                if (!ok || *abort_flag != 0u)
+                    break;
+#else
                 if (barrier_any(1, NTS, !ok || *abort_flag != 0u)) {
                     if (bad)
                         *abort_flag = 1u;
                     break;
                 }
+#endif
                 int      v   = vb + tid_s;
                 uint32_t pos = static_cast<uint32_t>(v) % ring_vecs;
+#if !(FLASHLLM_ABLATE & 8)
                 for (; v < ve; v += NTS) {
                     const uint4 w = lds16(ring_base + pos * 16u);
+#if (FLASHLLM_ABLATE & 2)
+                    if ((w.x ^ w.y ^ w.z ^ w.w) == 0x9E3779B9u)  // keeps the loads alive; practically never true
+                        scatter_word(stage, w.x);
+#else
                     scatter_word(stage, w.x);
                     scatter_word(stage, w.y);
                     scatter_word(stage, w.z);
                     scatter_word(stage, w.w);
+#endif
                     pos += NTS;
                     if (pos >= ring_vecs)
                         pos -= ring_vecs;
                 }
+#endif
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {

@@ -35,6 +35,7 @@ struct SpmmPlan {
     int ring_slots;     // compressed-stream ring: slots ...
     int chunk_vectors;  // ... of this many 16-byte vectors (power of two)
     int scatter_warps;  // 4 or 8
+    int offsets_staged; // TileOffsets entries a CTA may stage in shared memory (0 = read them from global memory)
     int smem_bytes;     // dynamic shared memory of the launch
 };
 
