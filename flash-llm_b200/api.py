@@ -60,9 +60,9 @@ def library() -> C.CDLL:
                                                C.c_int]
     L.FlashLLM_SplitK_Reduction.restype = C.c_int
     L.FlashLLM_SplitK_Reduction.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
-    L.FlashLLM_SetPlan.argtypes = [C.c_int] * 7
+    L.FlashLLM_SetPlan.argtypes = [_i32p, C.c_int]
     L.FlashLLM_GetPlan.restype = C.c_int
-    L.FlashLLM_GetPlan.argtypes = [C.c_int] * 4 + [_i32p]
+    L.FlashLLM_GetPlan.argtypes = [C.c_int] * 4 + [_i32p, C.c_int]
     L.FlashLLM_ConsumeStatus.restype = C.c_uint
     L.FlashLLM_LaunchCount.restype = C.c_ulonglong
     _lib = L
@@ -151,19 +151,23 @@ def encode_on_device(stream: int, A_d: int, M: int, K: int, alloc_i32, alloc_u32
     return comp_owner, offs_owner, T + 2, words
 
 
-def set_plan(cluster_k=0, workspace_k=0, a_stages=0, b_stages=0, ring_slots=0, chunk_vectors=0, scatter_warps=0):
-    """Pin the launch plan for later calls (0 = automatic)."""
-    library().FlashLLM_SetPlan(cluster_k, workspace_k, a_stages, b_stages, ring_slots, chunk_vectors, scatter_warps)
+PLAN_FIELDS = ("cluster_k", "workspace_k", "a_stages", "b_stages", "b_batch", "ring_slots", "chunk_vectors",
+               "scatter_groups", "warps_per_group", "producers")
 
 
-_PLAN_FIELDS = ("cluster_k", "workspace_k", "a_stages", "b_stages", "ring_slots", "chunk_vectors", "scatter_warps",
-                "smem_bytes")
+def set_plan(**fields: int) -> None:
+    """Pin launch-plan fields for later calls (absent or 0 = automatic); ``set_plan()`` restores the defaults."""
+    unknown = set(fields) - set(PLAN_FIELDS)
+    if unknown:
+        raise TypeError(f"unknown plan fields {sorted(unknown)}; known: {PLAN_FIELDS}")
+    values = (C.c_int * len(PLAN_FIELDS))(*[int(fields.get(name, 0)) for name in PLAN_FIELDS])
+    library().FlashLLM_SetPlan(values, len(PLAN_FIELDS))
 
 
 def get_plan(M: int, N: int, K: int, Split_K: int = 1) -> dict:
-    out = (C.c_int * 8)()
-    _check(library().FlashLLM_GetPlan(M, N, K, Split_K, out), "GetPlan")
-    return dict(zip(_PLAN_FIELDS, list(out)))
+    out = (C.c_int * (len(PLAN_FIELDS) + 1))()
+    _check(library().FlashLLM_GetPlan(M, N, K, Split_K, out, len(PLAN_FIELDS) + 1), "GetPlan")
+    return dict(zip(PLAN_FIELDS + ("smem_bytes",), list(out)))
 
 
 def consume_status() -> int:

@@ -109,7 +109,7 @@ static cudaError_t load_encode_tiled()
 // ---------------------------------------------------------------- launch plan
 
 struct PlanOverride {
-    int cluster_k = 0, workspace_k = 0, a_stages = 0, b_stages = 0, ring_slots = 0, chunk_vectors = 0, scatter_warps = 0;
+    int v[kPlanFieldCount] = {0};
 };
 static PlanOverride g_override;
 static std::mutex   g_override_mutex;
@@ -122,7 +122,7 @@ static int n_tile_for(int N)
 static int plan_smem_bytes(const SpmmPlan& pl)
 {
     const int bars = 8 * (2 * pl.ring_slots + 2 * pl.a_stages + 2 * pl.b_stages + 1) + 16 + 4 * pl.offsets_staged;
-    return 1024 /* alignment slack */ + pl.a_stages * kDenseTileBytes + pl.b_stages * pl.n_tile * kTileK * 2
+    return 1024 /* alignment slack */ + pl.a_stages * kDenseTileBytes + pl.b_stages * pl.b_batch * pl.n_tile * kTileK * 2
            + pl.ring_slots * pl.chunk_vectors * 16 + bars;
 }
 
@@ -147,24 +147,30 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     const int k_tiles   = K / kTileK;
     const int n_tiles   = (N + pl.n_tile - 1) / pl.n_tile;
     const int ctas_flat = tile_rows * n_tiles;
+    const int slab      = pl.n_tile * kTileK * 2;
 
-    pl.scatter_warps = ov.scatter_warps ? ov.scatter_warps : 8;
-    pl.chunk_vectors = ov.chunk_vectors ? ov.chunk_vectors : 256;
-    pl.ring_slots    = ov.ring_slots ? ov.ring_slots : (kMaxTileVectors / pl.chunk_vectors + 2);
-    pl.a_stages      = ov.a_stages ? ov.a_stages : 3;
-    pl.b_stages      = ov.b_stages ? ov.b_stages : (pl.n_tile <= 32 ? 4 : 3);
+    pl.scatter_groups  = ov.v[kPlanScatterGroups] ? ov.v[kPlanScatterGroups] : 4;
+    pl.warps_per_group = ov.v[kPlanWarpsPerGroup] ? ov.v[kPlanWarpsPerGroup] : 2;
+    pl.producers       = ov.v[kPlanProducers] ? ov.v[kPlanProducers] : 2;
+    pl.chunk_vectors   = ov.v[kPlanChunkVectors] ? ov.v[kPlanChunkVectors] : 512;
+    pl.ring_slots      = ov.v[kPlanRingSlots] ? ov.v[kPlanRingSlots] : (kMaxTileVectors / pl.chunk_vectors + 1);
+    if (!ov.v[kPlanRingSlots])
+        pl.ring_slots = (pl.ring_slots + pl.producers - 1) / pl.producers * pl.producers;
+    pl.a_stages        = ov.v[kPlanAStages] ? ov.v[kPlanAStages] : (pl.scatter_groups > 3 ? pl.scatter_groups : 3);
+    pl.b_batch         = ov.v[kPlanBBatch] ? ov.v[kPlanBBatch] : (4096 / slab > 0 ? 4096 / slab : 1);
+    pl.b_stages        = ov.v[kPlanBStages] ? ov.v[kPlanBStages] : 3;
 
-    // Enough CTAs for two per SM and about two waves, but never more K parts than K tiles.
-    const int target = st->sm_count * 4;
+    // Enough CTAs for two per SM, but never more K parts than K tiles.
+    const int target = st->sm_count * 2;
     int       want   = (target + ctas_flat - 1) / ctas_flat;
     if (want < 1)
         want = 1;
     if (want > k_tiles)
         want = k_tiles;
-    pl.cluster_k = ov.cluster_k ? ov.cluster_k : (want < kMaxClusterK ? want : kMaxClusterK);
+    pl.cluster_k = ov.v[kPlanClusterK] ? ov.v[kPlanClusterK] : (want < kMaxClusterK ? want : kMaxClusterK);
     if (pl.cluster_k > k_tiles)
         pl.cluster_k = k_tiles;
-    int extra = ov.workspace_k ? ov.workspace_k : (want + pl.cluster_k - 1) / pl.cluster_k;
+    int extra = ov.v[kPlanWorkspaceK] ? ov.v[kPlanWorkspaceK] : (want + pl.cluster_k - 1) / pl.cluster_k;
     if (extra > Split_K / 2)
         extra = Split_K / 2;  // the workspace is promised to hold Split_K fp16 matrices = Split_K/2 fp32 partials
     if (extra * pl.cluster_k > k_tiles)
@@ -179,12 +185,17 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
     pl.smem_bytes     = plan_smem_bytes(pl);
 
-    const bool ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8) && is_pow2(pl.chunk_vectors)
+    const int  scatter_warps = pl.scatter_groups * pl.warps_per_group;
+    const bool ok = (scatter_warps == 4 || scatter_warps == 8) && pl.scatter_groups >= 1 && pl.warps_per_group >= 1
+                    && pl.producers >= 1 && pl.producers <= kMaxProducers && is_pow2(pl.chunk_vectors)
                     && pl.chunk_vectors >= 64 && pl.ring_slots <= kMaxRingSlots
+                    // a slot is always refilled by the same producer warp, and a stage's successive tiles are taken by
+                    // groups that cannot be two uses ahead: both keep every mbarrier parity wait within one phase
+                    && pl.ring_slots % pl.producers == 0 && pl.a_stages >= pl.scatter_groups
                     && pl.ring_slots * pl.chunk_vectors >= kMaxTileVectors + pl.chunk_vectors
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
-                    && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK && pl.workspace_k >= 1
-                    && pl.smem_bytes <= st->smem_optin
+                    && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
+                    && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
                     // the fp32 partial tile of the cluster reduction is parked over the pipeline buffers
                     && pl.smem_bytes - 2048 - 4 * pl.offsets_staged >= pl.n_tile * kTileM * 4;
     if (!ok)
@@ -201,7 +212,7 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cudaLaunchConfig_t  cfg{};
     cudaLaunchAttribute attr[1];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
-    cfg.blockDim         = dim3((kControlWarps + pl.scatter_warps) * 32, 1, 1);
+    cfg.blockDim         = dim3((pl.producers + 2 + pl.scatter_groups * pl.warps_per_group) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream           = stream;
     attr[0].id               = cudaLaunchAttributeClusterDimension;
@@ -293,13 +304,16 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     params.K            = K_Global;
     params.k_tiles      = K_Global / kTileK;
 
-    // B as a 2-D tensor {K (inner), N}; one box = 64 K-elements x n_tile rows, 128-byte swizzle, rows past N read as 0.
+    // B as a 3-D tensor {64 K-elements (inner), N, K/64}: one box = b_batch K tiles of [n_tile x 64], each stored as
+    // a 128-byte-swizzled slab; rows past N and K tiles past K/64 read as 0.
     CUtensorMap      tmap;
-    const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(K_Global), static_cast<cuuint64_t>(N_Global)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K_Global) * 2};
-    const cuuint32_t box[2]     = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(pl.n_tile)};
-    const cuuint32_t estr[2]    = {1, 1};
-    const CUresult   cres       = g_encode_tiled(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(B), dims,
+    const cuuint64_t dims[3]    = {static_cast<cuuint64_t>(kTileK), static_cast<cuuint64_t>(N_Global),
+                                   static_cast<cuuint64_t>(K_Global / kTileK)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(K_Global) * 2, static_cast<cuuint64_t>(kTileK) * 2};
+    const cuuint32_t box[3]     = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(pl.n_tile),
+                                   static_cast<cuuint32_t>(pl.b_batch)};
+    const cuuint32_t estr[3]    = {1, 1, 1};
+    const CUresult   cres       = g_encode_tiled(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<half*>(B), dims,
                                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cres != CUDA_SUCCESS)
@@ -357,20 +371,14 @@ int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Works
                                              static_cast<const half*>(Reduction_Workspace), count, Split_K));
 }
 
-void FlashLLM_SetPlan(int cluster_k, int workspace_k, int a_stages, int b_stages, int ring_slots, int chunk_vectors,
-                      int scatter_warps)
+void FlashLLM_SetPlan(const int* fields, int count)
 {
     std::lock_guard<std::mutex> lock(g_override_mutex);
-    g_override.cluster_k     = cluster_k;
-    g_override.workspace_k   = workspace_k;
-    g_override.a_stages      = a_stages;
-    g_override.b_stages      = b_stages;
-    g_override.ring_slots    = ring_slots;
-    g_override.chunk_vectors = chunk_vectors;
-    g_override.scatter_warps = scatter_warps;
+    for (int i = 0; i < kPlanFieldCount; ++i)
+        g_override.v[i] = (fields != nullptr && i < count) ? fields[i] : 0;
 }
 
-int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out)
+int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count)
 {
     if (out == nullptr || !n_supported(N) || M <= 0 || K <= 0 || M % kTileM != 0 || K % kTileK != 0 || Split_K < 1)
         return static_cast<int>(cudaErrorInvalidValue);
@@ -381,14 +389,11 @@ int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out)
     SpmmPlan pl{};
     if ((err = make_plan(st, M, N, K, Split_K, &pl)) != cudaSuccess)
         return static_cast<int>(err);
-    out[0] = pl.cluster_k;
-    out[1] = pl.workspace_k;
-    out[2] = pl.a_stages;
-    out[3] = pl.b_stages;
-    out[4] = pl.ring_slots;
-    out[5] = pl.chunk_vectors;
-    out[6] = pl.scatter_warps;
-    out[7] = pl.smem_bytes;
+    const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k,   pl.a_stages,       pl.b_stages,
+                                             pl.b_batch,    pl.ring_slots,    pl.chunk_vectors,  pl.scatter_groups,
+                                             pl.warps_per_group, pl.producers, pl.smem_bytes};
+    for (int i = 0; i < count && i <= kPlanFieldCount; ++i)
+        out[i] = values[i];
     return 0;
 }
 
@@ -407,6 +412,15 @@ unsigned int FlashLLM_ConsumeStatus(void)
         cudaMemset(st->status, 0, sizeof(value));
     return value;
 }
+
+#ifdef FLASHLLM_TRACE
+// Timeline builds only: copies the recorded timestamps (kinds x depth) to the host.
+int FlashLLM_DebugTrace(long long* out, int count)
+{
+    cudaDeviceSynchronize();
+    return static_cast<int>(cudaMemcpyFromSymbol(out, flashllm::g_trace, sizeof(long long) * count));
+}
+#endif
 
 unsigned long long FlashLLM_LaunchCount(void)
 {

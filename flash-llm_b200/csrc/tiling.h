@@ -14,29 +14,48 @@ constexpr int kMaxTileVectors = kTileM * kTileK / kVectorWords;  // a fully dens
 constexpr int kDenseTileBytes = kTileM * kTileK * 2;             // 16 KB decompressed fp16 tile
 constexpr int kUmmaK          = 16;                              // K extent of one tcgen05.mma (fp16)
 
-constexpr int kMaxAStages   = 8;
-constexpr int kMaxBStages   = 8;
-constexpr int kMaxRingSlots = 32;
-constexpr int kMaxClusterK  = 8;    // portable cluster size limit
-constexpr int kControlWarps = 2;    // warp 0: copy producer, warp 1: MMA issuer + TMEM owner
+constexpr int kMaxAStages      = 12;
+constexpr int kMaxBStages      = 8;
+constexpr int kMaxRingSlots    = 64;
+constexpr int kMaxClusterK     = 8;   // portable cluster size limit
+constexpr int kMaxProducers    = 4;   // warps issuing bulk copies of the compressed stream
 constexpr int kMaxScatterWarps = 8;
-constexpr int kMaxThreads   = (kControlWarps + kMaxScatterWarps) * 32;
+// warps: [0, producers) copy producers, then one B-tile loader, then the MMA issuer / TMEM owner, then scatter warps
+constexpr int kMaxThreads = (kMaxProducers + 2 + kMaxScatterWarps) * 32;
 
 // Status bits written by kernels into the per-device status word.
-constexpr unsigned kStatusWaitExpired      = 1u;  // a bounded mbarrier wait ran out
-constexpr unsigned kStatusBadTileOffsets   = 2u;  // a tile's vector range was negative or above 2048
+constexpr unsigned kStatusWaitExpired    = 1u;  // a bounded mbarrier wait ran out
+constexpr unsigned kStatusBadTileOffsets = 2u;  // a tile's vector range was negative or above 2048
+
+// Fields of FlashLLM_SetPlan / FlashLLM_GetPlan, in this order.
+enum PlanField {
+    kPlanClusterK = 0,    // K parts reduced inside a cluster through distributed shared memory (1..8)
+    kPlanWorkspaceK,      // K parts reduced through the caller's workspace
+    kPlanAStages,         // decompressed 128x64 tiles in flight
+    kPlanBStages,         // B batches in flight
+    kPlanBBatch,          // K tiles of B fetched by one TMA instruction
+    kPlanRingSlots,       // compressed-stream ring: slots ...
+    kPlanChunkVectors,    // ... of this many 16-byte vectors (power of two)
+    kPlanScatterGroups,   // groups of scatter warps; each group decompresses whole tiles on its own
+    kPlanWarpsPerGroup,   // warps in a scatter group
+    kPlanProducers,       // warps issuing the bulk copies
+    kPlanFieldCount
+};
 
 struct SpmmPlan {
-    int n_tile;         // MMA N: 16, 32, 64 or 128
-    int cluster_k;      // K parts reduced inside a cluster through distributed shared memory
-    int workspace_k;    // K parts reduced through the caller's fp16 workspace
-    int a_stages;       // decompressed 128x64 tiles in flight
-    int b_stages;       // B tiles in flight
-    int ring_slots;     // compressed-stream ring: slots ...
-    int chunk_vectors;  // ... of this many 16-byte vectors (power of two)
-    int scatter_warps;  // 4 or 8
-    int offsets_staged; // TileOffsets entries a CTA may stage in shared memory (0 = read them from global memory)
-    int smem_bytes;     // dynamic shared memory of the launch
+    int n_tile;  // MMA N: 16, 32, 64 or 128
+    int cluster_k;
+    int workspace_k;
+    int a_stages;
+    int b_stages;
+    int b_batch;
+    int ring_slots;
+    int chunk_vectors;
+    int scatter_groups;
+    int warps_per_group;
+    int producers;
+    int offsets_staged;  // TileOffsets entries a CTA may stage in shared memory (0 = read them from global memory)
+    int smem_bytes;      // dynamic shared memory of the launch
 };
 
 }  // namespace flashllm

@@ -110,16 +110,22 @@ int FlashLLM_EncodeOnDevice_Pack(void* stream, const void* A_d, int M, int K, co
 int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K);
 
 /* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
- * csrc/SpMM_API.cu:79-118): fixes the launch plan for subsequent calls from this process; 0 = choose
- * automatically.  cluster_k: K parts summed inside a cluster (1..8); workspace_k: extra K parts through
- * Reduction_Workspace (capped at Split_K/2 of the call, as each fp32 partial matrix takes two fp16 ones' room); a_stages / b_stages: dense-tile and B-tile pipeline
- * depth; ring_slots x chunk_vectors(16 B each): compressed-stream ring; scatter_warps: 4 or 8. */
-void FlashLLM_SetPlan(int cluster_k, int workspace_k, int a_stages, int b_stages, int ring_slots, int chunk_vectors,
-                      int scatter_warps);
+ * csrc/SpMM_API.cu:79-118): fixes launch-plan fields for subsequent calls from this process.  `fields` holds up to
+ * ten ints, 0 = choose automatically, in this order:
+ *   0 cluster_k       K parts summed inside a thread-block cluster through distributed shared memory (1..8)
+ *   1 workspace_k     extra K parts through Reduction_Workspace (capped at Split_K/2 of the call: an fp32 partial
+ *                     matrix takes the room of two fp16 ones)
+ *   2 a_stages        decompressed 128x64 tiles in flight        3 b_stages  B batches in flight
+ *   4 b_batch         K tiles of B per TMA instruction
+ *   5 ring_slots x 6 chunk_vectors (16 bytes each, power of two): the compressed-stream ring
+ *   7 scatter_groups x 8 warps_per_group: decompression warps (4 or 8 in total)
+ *   9 producers       warps issuing the bulk copies (1..4)
+ * FlashLLM_SetPlan(nullptr, 0) restores automatic choice. */
+void FlashLLM_SetPlan(const int* fields, int count);
 
-/* Describes the plan the next SpMM call with these sizes would use; fills out[0..7] =
- * {cluster_k, workspace_k, a_stages, b_stages, ring_slots, chunk_vectors, scatter_warps, dynamic smem bytes}. */
-int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out);
+/* Describes the plan the next SpMM call with these sizes would use: out[0..9] as above, out[10] = dynamic shared
+ * memory in bytes; `count` = entries available in `out`. */
+int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count);
 
 /* Reads and clears the device-side status word of the current device (synchronises the device).  0 = no kernel of
  * this library gave up on a bounded wait or met a malformed TileOffsets since the last call. */

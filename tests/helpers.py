@@ -31,9 +31,20 @@ def error_metrics(got: np.ndarray, want: np.ndarray) -> tuple[float, float]:
     return rel, ab
 
 
-def assert_close(got: np.ndarray, want: np.ndarray, what: str = "") -> None:
+def assert_close(got: np.ndarray, want: np.ndarray, what: str = "", fp16_partials: int = 0) -> None:
+    """``fp16_partials`` = number of fp16-rounded partial sums inside ``want`` (the reference kernel and its CPU
+    model round every split-K part to fp16 before adding them, reference csrc/SpMM_Kernel.cuh:385): each adds up to
+    half an fp16 ulp of a partial, 2^-11 of the output scale, that no other implementation can reproduce."""
     rel, ab = error_metrics(got, want)
-    assert rel <= REL_TOL and ab <= ABS_TOL_OF_MAX, f"{what}: max rel err {rel:.3e}, max abs/peak {ab:.3e}"
+    if fp16_partials:
+        w = want.astype(np.float64)
+        g = got.astype(np.float64)
+        rms = float(np.sqrt(np.mean(w * w)))
+        slack = fp16_partials * 2.0 ** -11 * float(np.max(np.abs(w)))
+        excess = np.abs(g - w) - slack
+        rel = float(np.max(np.maximum(excess, 0.0) / np.maximum(np.abs(w), max(0.05 * rms, 1e-30))))
+    assert rel <= REL_TOL and ab <= ABS_TOL_OF_MAX * (1 + fp16_partials), \
+        f"{what}: max rel err {rel:.3e}, max abs/peak {ab:.3e}"
 
 
 class DeviceProblem:
