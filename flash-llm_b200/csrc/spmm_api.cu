@@ -45,10 +45,29 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 static EncodeTiledFn  g_encode_tiled = nullptr;
 static std::once_flag g_encode_once;
 
-template<int N_TILE>
-static cudaError_t raise_smem_limit(int bytes)
+template<int N_TILE, int GW>
+static cudaError_t raise_smem_limit_one(int optin)
 {
-    return cudaFuncSetAttribute(spmm_tcgen05_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    cudaFuncAttributes attr{};
+    cudaError_t        e = cudaFuncGetAttributes(&attr, spmm_tcgen05_kernel<N_TILE, GW>);
+    if (e != cudaSuccess)
+        return e;
+    // the opt-in limit covers static and dynamic shared memory together
+    return cudaFuncSetAttribute(spmm_tcgen05_kernel<N_TILE, GW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                optin - static_cast<int>(attr.sharedSizeBytes));
+}
+
+template<int N_TILE>
+static cudaError_t raise_smem_limit(int optin)
+{
+    cudaError_t e = raise_smem_limit_one<N_TILE, 1>(optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_one<N_TILE, 2>(optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_one<N_TILE, 4>(optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_one<N_TILE, 8>(optin);
+    return e;
 }
 
 static DeviceState* device_state(cudaError_t* err)
@@ -122,7 +141,7 @@ static int n_tile_for(int N)
 static int plan_smem_bytes(const SpmmPlan& pl)
 {
     const int bars = 8 * (2 * pl.ring_slots + 2 * pl.a_stages + 2 * pl.b_stages + 1) + 16 + 4 * pl.offsets_staged;
-    return 1024 /* alignment slack */ + pl.a_stages * kDenseTileBytes + pl.b_stages * pl.b_batch * pl.n_tile * kTileK * 2
+    return pl.a_stages * kDenseTileBytes + pl.b_stages * pl.b_batch * pl.n_tile * kTileK * 2
            + pl.ring_slots * pl.chunk_vectors * 16 + bars;
 }
 
@@ -186,7 +205,9 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     pl.smem_bytes     = plan_smem_bytes(pl);
 
     const int  scatter_warps = pl.scatter_groups * pl.warps_per_group;
-    const bool ok = (scatter_warps == 4 || scatter_warps == 8) && pl.scatter_groups >= 1 && pl.warps_per_group >= 1
+    const bool ok = (scatter_warps == 4 || scatter_warps == 8) && pl.scatter_groups >= 1
+                    && (pl.warps_per_group == 1 || pl.warps_per_group == 2 || pl.warps_per_group == 4
+                        || pl.warps_per_group == 8)
                     && pl.producers >= 1 && pl.producers <= kMaxProducers && is_pow2(pl.chunk_vectors)
                     && pl.chunk_vectors >= 64 && pl.ring_slots <= kMaxRingSlots
                     // a slot is always refilled by the same producer warp, and a stage's successive tiles are taken by
@@ -197,7 +218,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
                     && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
                     // the fp32 partial tile of the cluster reduction is parked over the pipeline buffers
-                    && pl.smem_bytes - 2048 - 4 * pl.offsets_staged >= pl.n_tile * kTileM * 4;
+                    && pl.smem_bytes - 1024 - 4 * pl.offsets_staged >= pl.n_tile * kTileM * 4;
     if (!ok)
         return cudaErrorInvalidConfiguration;
     *out = pl;
@@ -222,7 +243,12 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cfg.attrs                = attr;
     cfg.numAttrs             = 1;
     count_launch();
-    return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
+    switch (pl.warps_per_group) {
+        case 1: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 1>, tmap, params);
+        case 2: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 2>, tmap, params);
+        case 4: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 4>, tmap, params);
+        default: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 8>, tmap, params);
+    }
 }
 
 static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws, long long count, int parts)

@@ -49,15 +49,23 @@ constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
 #ifndef FLASHLLM_ABLATE
 #define FLASHLLM_ABLATE 0
 #endif
+#ifndef FLASHLLM_RELAXED_SLEEP_NS
+#define FLASHLLM_RELAXED_SLEEP_NS 40
+#endif
 
 // Timeline builds (never the shipped one) record SM-clock timestamps of pipeline events of one CTA.
 #ifdef FLASHLLM_TRACE
-constexpr int kTraceKinds = 24, kTraceDepth = 256;
+// Timestamps go to shared memory (a global store would sit in front of every later release operation of the thread)
+// and are copied out when the CTA finishes.
+constexpr int kTraceKinds = 24, kTraceDepth = 96;
 __device__ long long g_trace[kTraceKinds * kTraceDepth];
+__device__ long long g_trace_origin;
+#define FL_TRACE_BASE 40
 #define FL_TRACE(kind, idx)                                                                                             \
     do {                                                                                                               \
-        if (blockIdx.y == FLASHLLM_TRACE && blockIdx.x == 0 && (idx) < kTraceDepth)                                    \
-            g_trace[(kind) * kTraceDepth + (idx)] = clock64();                                                         \
+        if (blockIdx.y == FLASHLLM_TRACE && blockIdx.x == 0 && (idx) >= FL_TRACE_BASE                                  \
+            && (idx) < FL_TRACE_BASE + kTraceDepth)                                                                    \
+            s_trace[(kind) * kTraceDepth + (idx) - FL_TRACE_BASE] = static_cast<unsigned int>(clock64());             \
     } while (0)
 #else
 #define FL_TRACE(kind, idx)                                                                                             \
@@ -99,6 +107,33 @@ wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsig
     }
 }
 
+// Same wait for the roles that are not on the critical path (scatter groups, copy producers): sleeps between probes so
+// that the spinning does not take issue slots from the MMA-issuing thread, whose per-tile loop is the pacing chain.
+__device__ __forceinline__ bool
+wait_bounded_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int* status)
+{
+    if (ptx::mbar_test_wait(bar, parity))
+        return true;
+    uint64_t t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+        __nanosleep(FLASHLLM_RELAXED_SLEEP_NS);
+        if (ptx::mbar_test_wait(bar, parity))
+            return true;
+        if ((it & 1023u) == 0u) {
+            if (*abort_flag)
+                return false;
+            const uint64_t now = ptx::globaltimer_ns();
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1u;
+                atomicOr(status, kStatusWaitExpired);
+                return false;
+            }
+        }
+    }
+}
+
 // Warp-collective form: lane 0 alone probes the mbarrier and the other lanes take its answer at a warp barrier.
 // A probe executed by all 32 lanes costs several hundred cycles (measured: ~380 per already-completed wait), so a
 // warp must never wait lane by lane.  The warp barrier orders lane 0's observation of the completed phase before
@@ -108,7 +143,7 @@ wait_bounded_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, 
 {
     uint32_t ok = 1;
     if ((threadIdx.x & 31) == 0)
-        ok = wait_bounded(bar, parity, abort_flag, status) ? 1u : 0u;
+        ok = wait_bounded_relaxed(bar, parity, abort_flag, status) ? 1u : 0u;
     return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
 }
 
@@ -160,15 +195,34 @@ __device__ __forceinline__ void scatter_vector(uint32_t stage, const uint4& w)
     scatter_word(stage, w.w);
 }
 
-template<int N_TILE>
+// Zeroes one 16 KB stage with the GW*32 threads of a scatter group, fully unrolled: 32 / 16 / 8 stores per thread.
+template<int GW>
+__device__ __forceinline__ void zero_fill_stage(uint32_t stage, int gtid)
+{
+    constexpr int kPerThread = kDenseTileBytes / (GW * 32 * 16);
+#pragma unroll
+    for (int q = 0; q < kPerThread; ++q)
+        sts_zero16(stage + static_cast<uint32_t>(q * GW * 32 + gtid) * 16u);
+}
+
+// N_TILE: MMA N (tokens per CTA).  GW: warps per scatter group (compile-time so that the per-tile code is straight
+// line: the per-tile paths are latency-bound chains of a few dozen instructions, and every loop-carried branch or
+// runtime division in them costs more than the work it guards).
+template<int N_TILE, int GW>
 __global__ void __launch_bounds__(kMaxThreads, 1)
     spmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_b, const SpmmParams p)
 {
     static_assert(N_TILE == 16 || N_TILE == 32 || N_TILE == 64 || N_TILE == 128, "unsupported MMA N");
+    static_assert(GW == 1 || GW == 2 || GW == 4 || GW == 8, "unsupported scatter group size");
     constexpr uint32_t kBSlab    = N_TILE * kTileK * 2;  // one K tile of B in shared memory
     constexpr uint32_t kTmemCols = N_TILE < 32 ? 32 : N_TILE;
 
-    extern __shared__ uint8_t smem_raw[];
+#ifdef FLASHLLM_TRACE
+    __shared__ unsigned int s_trace[kTraceKinds * kTraceDepth];
+    for (int i = threadIdx.x; i < kTraceKinds * kTraceDepth; i += blockDim.x)
+        s_trace[i] = 0;
+#endif
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t            raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t            base     = (raw_addr + 1023u) & ~1023u;  // swizzled operands need 1024-byte alignment
     uint8_t* const            smem     = smem_raw + (base - raw_addr);
@@ -186,7 +240,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     const int       G          = plan.workspace_k;
     const int       P          = plan.producers;
     const int       NG         = plan.scatter_groups;
-    const int       GW         = plan.warps_per_group;
     const int       NSW        = NG * GW;
     const int       NTS        = NSW * 32;
     const int       b_warp     = P;      // warp that loads B
@@ -210,7 +263,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     const uint32_t misc_off   = (acc_full + 8u) - base;
     volatile uint32_t* const tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem + misc_off);
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(smem + misc_off + 4);
-    volatile int* const      chunks_released = reinterpret_cast<volatile int*>(smem + misc_off + 8);
+    volatile int* const      tiles_scattered = reinterpret_cast<volatile int*>(smem + misc_off + 8);
     int* const               offs_stage = reinterpret_cast<int*>(smem + misc_off + 16);  // plan.offsets_staged ints
 
     // ---- work assignment: blockIdx.x = K part inside the cluster, y = tile row, z = (N tile, workspace part)
@@ -226,6 +279,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     const int* const offs_global = p.tile_offsets + static_cast<long long>(tile_row) * p.k_tiles + k_begin;
     const bool       staged      = (L + 1 <= plan.offsets_staged);
     const int* const offs        = staged ? offs_stage : offs_global;  // valid after the set-up barrier
+
+    if (raw_addr != base) {  // the launch did not honour the 1024-byte alignment: nothing below would be valid
+        if (threadIdx.x == 0)
+            atomicOr(p.status, kStatusSmemMisaligned);
+        return;
+    }
 
     // ---- set-up
     if (threadIdx.x == 0) {
@@ -245,7 +304,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         }
         ptx::mbar_init(acc_full, 1);
         *abort_flag      = (status_now != 0u) ? 1u : 0u;
-        *chunks_released = 0;
+        *tiles_scattered = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_b);
     }
@@ -277,7 +336,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
             uint32_t     use     = warp / ring_slots;
             for (int c = warp; c < nchunks; c += P) {
                 FL_TRACE(11, c);
-                if (!wait_bounded(ring_empty + 8u * slot, (use & 1u) ^ 1u, abort_flag, p.status))
+                if (!wait_bounded_relaxed(ring_empty + 8u * slot, (use & 1u) ^ 1u, abort_flag, p.status))
                     break;
                 FL_TRACE(12, c);
                 const int      left  = nvec - (c << cv_shift);
@@ -310,7 +369,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         if (lane == 1 && L > 0) {  // timeline builds: a monitor thread timestamps the landing of every chunk
             const int nvec_m    = offs[L] - offs[0];
             const int nchunks_m = (nvec_m + CV - 1) >> cv_shift;
-            for (int c = 0; c < nchunks_m && c < kTraceDepth; ++c) {
+            for (int c = 0; c < nchunks_m && c < FL_TRACE_BASE + kTraceDepth; ++c) {
                 if (!wait_bounded(ring_full + 8u * (c % ring_slots), static_cast<uint32_t>(c / ring_slots) & 1u,
                                   abort_flag, p.status))
                     break;
@@ -325,7 +384,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
             uint32_t  use     = 0;
             int       issued  = 0;
             for (int b = 0; b < batches; ++b) {
-                if (!wait_bounded(b_empty + 8u * bs, (use & 1u) ^ 1u, abort_flag, p.status))
+                if (!wait_bounded_relaxed(b_empty + 8u * bs, (use & 1u) ^ 1u, abort_flag, p.status))
                     break;
                 const uint32_t bar = b_full + 8u * bs;
                 ptx::mbar_arrive_expect_tx(bar, KB * kBSlab);
@@ -349,20 +408,51 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     }
     else if (warp == mma_warp) {
         // ================================================================ MMA issuer (tile order) + ring release
-        if (lane == 0 && L > 0) {
+        // The whole warp takes part in the waiting so that the barriers a tile needs are probed side by side (a probe
+        // is a shared-memory round trip of a hundred cycles or more; one after another they would pace the kernel).
+        // Lane 0 then issues the MMAs, commits, and hands ring chunks back.
+        if (L > 0) {
             const uint32_t idesc   = ptx::umma_idesc_f16_f32(kTileM, N_TILE);
             const int      v_first = offs[0];
+            // Descriptors differ only in the 16-byte-unit start address (low bits): build them once, then add.
+            const uint64_t a_desc0 = ptx::umma_desc_kmajor_sw128(a_base);
+            const uint64_t b_desc0 = ptx::umma_desc_kmajor_sw128(b_base);
             int            s = 0, bs = 0, kb = 0;
-            uint32_t       a_use = 0, b_use = 0;
+            uint32_t       a_par = 0, b_par = 0;
             int            released = 0, rel_slot = 0;
-            for (int j = 0; j < L; ++j) {
+            int            tile_end = offs[1];  // fetched one tile ahead of its use
+            bool           alive    = true;
+            for (int j = 0; j < L && alive; ++j) {
                 FL_TRACE(7, j);
-                if (!wait_bounded(a_full + 8u * s, a_use & 1u, abort_flag, p.status))
-                    break;
-                FL_TRACE(8, j);
-                // Tile j is decompressed: ring chunks that end at or before its last vector are free again.
-                const int done = (offs[j + 1] - v_first) >> cv_shift;
-                if (released < done) {
+                // lane 0 watches the decompressed tile, lane 1 the B batch (when this tile opens one)
+                const uint32_t my_bar = lane == 0 ? a_full + 8u * s : b_full + 8u * bs;
+                const uint32_t my_par = lane == 0 ? a_par : b_par;
+                const bool     mine   = lane == 0 || (lane == 1 && kb == 0 && !(FLASHLLM_ABLATE & 32));
+                bool           ready  = !mine || ptx::mbar_test_wait(my_bar, my_par);
+                if (!__all_sync(0xFFFFFFFFu, ready)) {
+                    if (mine && !ready)
+                        ready = wait_bounded(my_bar, my_par, abort_flag, p.status);
+                    if (!__all_sync(0xFFFFFFFFu, ready))
+                        break;
+                }
+                FL_TRACE(9, j);
+                const int next_end = (j + 2 <= L) ? offs[j + 2] : 0;  // in flight during the MMA issue
+                if (lane == 0) {
+                    ptx::tc_fence_after_sync();
+                    const uint64_t a_desc = a_desc0 + static_cast<uint32_t>(s * (kDenseTileBytes >> 4));
+                    const uint64_t b_desc = b_desc0 + static_cast<uint32_t>((bs * KB + kb) * (kBSlab >> 4));
+#pragma unroll
+                    for (int kk = 0; kk < ((FLASHLLM_ABLATE & 4) ? 0 : kTileK / kUmmaK); ++kk) {
+                        ptx::umma_f16_ss(tmem_acc, a_desc + kk * (kUmmaK * 2 >> 4), b_desc + kk * (kUmmaK * 2 >> 4), idesc,
+                                         (j | kk) != 0 ? 1u : 0u);
+                    }
+                    FL_TRACE(18, j);
+                    ptx::umma_commit(a_empty + 8u * s);
+                    if (kb + 1 == KB || j == L - 1)
+                        ptx::umma_commit(b_empty + 8u * bs);
+                    FL_TRACE(10, j);
+                    // Tile j is decompressed: ring chunks that end at or before its last vector are free again.
+                    const int done = (tile_end - v_first) >> cv_shift;
                     while (released < done) {
                         FL_TRACE(14, released);
                         ptx::mbar_arrive(ring_empty + 8u * rel_slot);
@@ -370,46 +460,32 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                         if (++rel_slot == ring_slots)
                             rel_slot = 0;
                     }
-                    *chunks_released = released;
+                    *tiles_scattered = j + 1;
+                    FL_TRACE(19, j);
                 }
-                if (kb == 0 && !(FLASHLLM_ABLATE & 32) && !wait_bounded(b_full + 8u * bs, b_use & 1u, abort_flag, p.status))
-                    break;
-                FL_TRACE(9, j);
-                ptx::tc_fence_after_sync();
-                const uint32_t a_addr = a_base + s * kDenseTileBytes;
-                const uint32_t b_addr = b_base + (bs * KB + kb) * kBSlab;
-#pragma unroll
-                for (int kk = 0; kk < ((FLASHLLM_ABLATE & 4) ? 0 : kTileK / kUmmaK); ++kk) {
-                    ptx::umma_f16_ss(tmem_acc,
-                                     ptx::umma_desc_kmajor_sw128(a_addr + kk * kUmmaK * 2),
-                                     ptx::umma_desc_kmajor_sw128(b_addr + kk * kUmmaK * 2),
-                                     idesc,
-                                     (j | kk) != 0 ? 1u : 0u);
-                }
-                ptx::umma_commit(a_empty + 8u * s);
-                FL_TRACE(10, j);
+                tile_end = next_end;
                 if (++s == a_stages) {
                     s = 0;
-                    ++a_use;
+                    a_par ^= 1u;
                 }
-                if (++kb == KB || j == L - 1) {
-                    ptx::umma_commit(b_empty + 8u * bs);
+                if (++kb == KB) {
                     kb = 0;
                     if (++bs == b_stages) {
                         bs = 0;
-                        ++b_use;
+                        b_par ^= 1u;
                     }
                 }
             }
-            ptx::umma_commit(acc_full);
+            if (lane == 0)
+                ptx::umma_commit(acc_full);
         }
     }
     else {
         // ================================================================ scatter groups: one whole tile at a time
-        const int sw   = warp - first_sw;  // scatter warp index
-        const int grp  = sw / GW;
-        const int gtid = (sw % GW) * 32 + lane;
-        const int GT   = GW * 32;
+        const int     sw   = warp - first_sw;  // scatter warp index
+        const int     grp  = sw / GW;
+        const int     gtid = (sw % GW) * 32 + lane;
+        constexpr int GT   = GW * 32;
         if (L > 0) {
             const int v_first = offs[0];
             // Stage and ring-slot indices advance by repeated subtraction: a runtime division costs the warp more than
@@ -419,43 +495,48 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
             int      cur_c    = 0;               // a chunk index at or before this tile's first chunk ...
             int      cur_slot = 0;               // ... and its ring slot and use count
             uint32_t cur_use  = 0;
+            int      vb_next  = grp < L ? offs[grp] - v_first : 0;  // offsets are fetched one tile ahead of their use
+            int      ve_next  = grp < L ? offs[grp + 1] - v_first : 0;
             for (int j = grp; j < L; j += NG, s += NG) {
                 if (s >= a_stages) {  // a_stages >= NG: one step is enough
                     s -= a_stages;
                     ++a_use;
                 }
-                const int      vb    = offs[j] - v_first;
-                const int      ve    = offs[j + 1] - v_first;
-                const uint32_t stage = a_base + s * kDenseTileBytes;
-                const bool     bad   = (ve < vb) || (ve - vb > kMaxTileVectors) || (vb < 0);
+                const int vb = vb_next, ve = ve_next;
+                if (j + NG < L) {
+                    vb_next = offs[j + NG] - v_first;
+                    ve_next = offs[j + NG + 1] - v_first;
+                }
+                // end of the newest tile whose MMA must have finished before this stage was handed back to us
+                const int      settled = j >= a_stages ? offs[j - a_stages + 1] - v_first : 0;
+                const uint32_t stage   = a_base + s * kDenseTileBytes;
+                const bool     bad     = (ve < vb) || (ve - vb > kMaxTileVectors) || (vb < 0);
                 if (bad)
                     atomicOr(p.status, kStatusBadTileOffsets);
                 if (gtid == 0)
                     FL_TRACE(0, j);
-                bool ok = !bad && wait_bounded_warp(a_empty + 8u * s, (a_use & 1u) ^ 1u, abort_flag, p.status);
-                if (gtid == 0)
-                    FL_TRACE(1, j);
-                if (ok && !(FLASHLLM_ABLATE & 1)) {
-                    for (uint32_t off = gtid * 16u; off < kDenseTileBytes; off += GT * 16u)
-                        sts_zero16(stage + off);
-                }
-                if (gtid == 0)
-                    FL_TRACE(2, j);
-                if (ok && ve > vb) {
-                    // Only the chunks this tile overlaps: they cannot be recycled before this tile is done.  A parity
-                    // wait is only meaningful once the slot's previous occupant has been handed back, so a group that
-                    // has run a whole ring ahead of the tile-order release first waits for that.
-                    const int c_first = vb >> cv_shift, c_last = (ve - 1) >> cv_shift;
-                    while (cur_c < c_first) {
-                        ++cur_c;
-                        if (++cur_slot == ring_slots) {
-                            cur_slot = 0;
-                            ++cur_use;
-                        }
+                // ---- everything this tile waits for, probed side by side: lane 0 the stage, lanes 1.. the ring chunks
+                const int c_first = vb >> cv_shift;
+                const int n_chunk = ve > vb ? (((ve - 1) >> cv_shift) - c_first + 1) : 0;
+                while (cur_c < c_first) {
+                    ++cur_c;
+                    if (++cur_slot == ring_slots) {
+                        cur_slot = 0;
+                        ++cur_use;
                     }
-                    if (c_last >= ring_slots && lane == 0) {
+                }
+                bool ok = !bad;
+                // A parity probe of a ring slot means something only once the slot's previous occupant has landed.
+                // That is certain when that occupant ends inside tiles whose MMA has already completed (which our
+                // stage hand-back proves); otherwise (very dense tiles) wait for the tile counter first.
+                const int c_last = c_first + n_chunk - 1;
+                if (ok && n_chunk > 0 && c_last >= ring_slots && ((c_last - ring_slots + 1) << cv_shift) > settled) {
+                    if (lane == 0) {
+                        int need = j;  // first tile index whose completion covers the previous occupant
+                        while (need > 0 && offs[need] - v_first >= ((c_last - ring_slots + 1) << cv_shift))
+                            --need;
                         uint64_t t0 = 0;
-                        for (uint32_t it = 1; *chunks_released <= c_last - ring_slots; ++it) {
+                        for (uint32_t it = 1; *tiles_scattered <= need; ++it) {
                             if ((it & 255u) == 0u) {
                                 const uint64_t now = ptx::globaltimer_ns();
                                 if (*abort_flag) {
@@ -474,39 +555,55 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                         }
                     }
                     ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0;
-                    int      w_slot = cur_slot;
-                    uint32_t w_use  = cur_use;
-                    if (gtid == 0)
-                        FL_TRACE(16, j);
-                    for (int c = c_first; c <= c_last && ok; ++c) {
-                        ok = wait_bounded_warp(ring_full + 8u * w_slot, w_use & 1u, abort_flag, p.status);
-                        if (gtid == 0 && c == c_first)
-                            FL_TRACE(17, j);
-                        if (++w_slot == ring_slots) {
-                            w_slot = 0;
-                            ++w_use;
+                }
+                if (ok) {
+                    uint32_t my_bar, my_par;
+                    bool     mine;
+                    if (lane == 0) {
+                        my_bar = a_empty + 8u * s;
+                        my_par = (a_use & 1u) ^ 1u;
+                        mine   = true;
+                    }
+                    else {
+                        int      slot = cur_slot + (lane - 1);
+                        uint32_t use  = cur_use;
+                        if (slot >= ring_slots) {  // a tile spans at most ring_slots chunks
+                            slot -= ring_slots;
+                            ++use;
                         }
+                        my_bar = ring_full + 8u * slot;
+                        my_par = use & 1u;
+                        mine   = lane - 1 < n_chunk;
+                    }
+                    bool ready = !mine || ptx::mbar_test_wait(my_bar, my_par);
+                    if (!__all_sync(0xFFFFFFFFu, ready)) {
+                        if (mine && !ready)
+                            ready = wait_bounded_relaxed(my_bar, my_par, abort_flag, p.status);
+                        ok = __all_sync(0xFFFFFFFFu, ready);
                     }
                 }
-                if (gtid == 0) {
+                if (gtid == 0)
                     FL_TRACE(3, j);
-#ifdef FLASHLLM_TRACE
-                    if (blockIdx.y == FLASHLLM_TRACE && blockIdx.x == 0 && j < kTraceDepth)
-                        g_trace[15 * kTraceDepth + j] = ve > vb ? ((ve - 1) >> cv_shift) : -1;
-#endif
-                }
+                if (ok && !(FLASHLLM_ABLATE & 1))
+                    zero_fill_stage<GW>(stage, gtid);
+                if (gtid == 0)
+                    FL_TRACE(2, j);
                 // Zeroes must be in place before any warp of the group scatters; the same barrier makes giving up
                 // unanimous inside the group.
+                bool give_up = !ok;
 #if (FLASHLLM_ABLATE & 16)
-                if (!ok || *abort_flag != 0u)
-                    break;
+                give_up = __any_sync(0xFFFFFFFFu, give_up);
 #else
-                if (barrier_any(1 + grp, GT, !ok || *abort_flag != 0u)) {
+                if (GW == 1)
+                    give_up = __any_sync(0xFFFFFFFFu, give_up);  // also orders the zero stores before the scatter
+                else
+                    give_up = barrier_any(1 + grp, GT, give_up);
+#endif
+                if (give_up) {
                     if (bad)
                         *abort_flag = 1u;
                     break;
                 }
-#endif
                 if (gtid == 0)
                     FL_TRACE(4, j);
 #if !(FLASHLLM_ABLATE & 8)
@@ -514,25 +611,35 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                 uint32_t pos = (static_cast<uint32_t>(cur_slot) << cv_shift) + (static_cast<uint32_t>(vb) & (CV - 1)) + gtid;
                 if (pos >= ring_vecs)
                     pos -= ring_vecs;  // GT <= CV <= ring_vecs: one step is enough
-                // two vectors per trip so that the second load is in flight while the first is being scattered
-                for (; v + GT < ve; v += 2 * GT) {
-                    uint32_t pos2 = pos + GT;
-                    if (pos2 >= ring_vecs)
-                        pos2 -= ring_vecs;
+                // four vectors per trip: the loads are issued together, then their sixteen stores
+                for (; v + 3 * GT < ve; v += 4 * GT) {
+                    uint32_t p1 = pos + GT;
+                    if (p1 >= ring_vecs)
+                        p1 -= ring_vecs;
+                    uint32_t p2 = p1 + GT;
+                    if (p2 >= ring_vecs)
+                        p2 -= ring_vecs;
+                    uint32_t p3 = p2 + GT;
+                    if (p3 >= ring_vecs)
+                        p3 -= ring_vecs;
                     const uint4 w0 = lds16(ring_base + pos * 16u);
-                    const uint4 w1 = lds16(ring_base + pos2 * 16u);
+                    const uint4 w1 = lds16(ring_base + p1 * 16u);
+                    const uint4 w2 = lds16(ring_base + p2 * 16u);
+                    const uint4 w3 = lds16(ring_base + p3 * 16u);
 #if (FLASHLLM_ABLATE & 2)
-                    if ((w0.x ^ w0.y ^ w1.z ^ w1.w) == 0x9E3779B9u)  // keeps the loads alive; practically never true
+                    if ((w0.x ^ w1.y ^ w2.z ^ w3.w) == 0x9E3779B9u)  // keeps the loads alive; practically never true
                         scatter_word(stage, w0.x);
 #else
                     scatter_vector(stage, w0);
                     scatter_vector(stage, w1);
+                    scatter_vector(stage, w2);
+                    scatter_vector(stage, w3);
 #endif
-                    pos = pos2 + GT;
+                    pos = p3 + GT;
                     if (pos >= ring_vecs)
                         pos -= ring_vecs;
                 }
-                if (v < ve) {
+                for (; v < ve; v += GT) {
                     const uint4 w0 = lds16(ring_base + pos * 16u);
 #if (FLASHLLM_ABLATE & 2)
                     if ((w0.x ^ w0.y ^ w0.z ^ w0.w) == 0x9E3779B9u)
@@ -540,6 +647,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 #else
                     scatter_vector(stage, w0);
 #endif
+                    pos += GT;
+                    if (pos >= ring_vecs)
+                        pos -= ring_vecs;
                 }
 #endif
                 if (gtid == 0)
@@ -642,6 +752,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         __syncwarp();
         ptx::tmem_dealloc(tmem_acc, kTmemCols);
     }
+#ifdef FLASHLLM_TRACE
+    if (blockIdx.y == FLASHLLM_TRACE && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < kTraceKinds * kTraceDepth; i += blockDim.x)
+            g_trace[i] = s_trace[i];
+#endif
 }
 
 // Sums the fp32 partial matrices this library parks in the caller's workspace when workspace_k > 1 and rounds once:

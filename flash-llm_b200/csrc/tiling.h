@@ -26,6 +26,7 @@ constexpr int kMaxThreads = (kMaxProducers + 2 + kMaxScatterWarps) * 32;
 // Status bits written by kernels into the per-device status word.
 constexpr unsigned kStatusWaitExpired    = 1u;  // a bounded mbarrier wait ran out
 constexpr unsigned kStatusBadTileOffsets = 2u;  // a tile's vector range was negative or above 2048
+constexpr unsigned kStatusSmemMisaligned = 16u; // dynamic shared memory did not start on a 1024-byte boundary
 
 // Fields of FlashLLM_SetPlan / FlashLLM_GetPlan, in this order.
 enum PlanField {
