@@ -35,8 +35,9 @@ sys.path.insert(0, ROOT)
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-# (name, M, K, reference's hand-tuned Split_K for the shape: kernel_benchmark/benchmark.sh:13-15)
-OPT66B_LAYER = [("qkv", 27648, 9216, 2), ("out_proj", 9216, 9216, 6), ("ffn1", 36864, 9216, 3), ("ffn2", 9216, 36864, 6)]
+# (name, M, K, Split_K hint of this library's arm, the reference's hand-tuned Split_K: kernel_benchmark/benchmark.sh:13-15)
+OPT66B_LAYER = [("qkv", 27648, 9216, 8, 2), ("out_proj", 9216, 9216, 8, 6), ("ffn1", 36864, 9216, 1, 3),
+                ("ffn2", 9216, 36864, 8, 6)]
 N_TOKENS = 16
 SPARSITY = 0.8
 SEED = 0xF1A50000
@@ -59,22 +60,29 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.window = index, [], None, (0.0, float("inf"))
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            deadline = time.time() + 5.0  # nvidia-smi needs a moment before its first line
+            while not self.rows and time.time() < deadline:
+                time.sleep(0.02)
         except OSError:
             self.proc = None
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def mark(self, t0: float, t1: float):
+        """Only samples taken between t0 and t1 (the timed region) count."""
+        self.window = (t0, t1)
 
     def __exit__(self, *exc):
         if self.proc:
@@ -83,10 +91,11 @@ class ClockSampler:
             self.thread.join(timeout=2)
 
     def summary(self) -> dict:
-        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        rows = [r for t, r in self.rows if self.window[0] <= t <= self.window[1]]
+        sm = [int(r[0]) for r in rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in rows if len(r) > 1 and r[1].isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -103,10 +112,11 @@ def physical_gpu_index(local_rank: int) -> int:
 class Layer:
     """One rank's row shard of the four weight matrices, encoded on the device, plus activations and outputs."""
 
-    def __init__(self, fl, rank: int, world: int, dev):
+    def __init__(self, fl, rank: int, world: int, dev, reference_splits: bool = False):
         self.fl, self.dev, self.items = fl, dev, []
         stream = torch.cuda.current_stream(dev).cuda_stream
-        for idx, (name, M, K, split_k) in enumerate(OPT66B_LAYER):
+        for idx, (name, M, K, split_ours, split_ref) in enumerate(OPT66B_LAYER):
+            split_k = split_ref if reference_splits else split_ours
             assert M % (128 * world) == 0, (name, M, world)
             rows = (rank * M // world, (rank + 1) * M // world)
             m = rows[1] - rows[0]
@@ -158,7 +168,7 @@ def cpu_baseline(sample_seconds: float = 12.0) -> dict:
     """Host fp32 dense GEMM (OpenMP, all host threads) on a row sample of the FFN1-shaped matrix."""
     import flash_llm_b200 as fl
     from oracle import cpu_oracle
-    name, M, K, _ = OPT66B_LAYER[2]
+    name, M, K, _, _ = OPT66B_LAYER[2]
     cores = os.cpu_count() or 1
     rows = 1024
     A = fl.synthetic.sparse_uniform_matrix(M, K, SPARSITY, SEED + 2, rows=(0, rows)).numpy()
@@ -188,7 +198,7 @@ def cpu_baseline(sample_seconds: float = 12.0) -> dict:
 
 def config_dict(world: int) -> dict:
     return {"workload": "OPT-66B decoder-layer SpMMs (27648x9216, 9216x9216, 36864x9216, 9216x36864), N=16 tokens, "
-                        "80% uniform-random sparsity, fp16, tiled-CSL, Split_K hints 2/6/3/6",
+                        "80% uniform-random sparsity, fp16, tiled-CSL, Split_K tuned per shape (ours 8/8/1/8, reference 2/6/3/6)",
             "sharding": f"weight rows split evenly over {world} GPU(s), no collective",
             "l2": "inputs larger than L2: each step streams ~821 MB of compressed weights (126 MB L2)",
             "tokens": N_TOKENS, "sparsity": SPARSITY}
@@ -229,13 +239,16 @@ def run_ours(args) -> None:
     barrier()
     launches_before = fl.launch_count()
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        t_begin = time.time()
         ms = time_loop(lambda: layer.step(stream), args.steps, dev)
+        clocks.mark(t_begin, time.time())
+        time.sleep(0.05)
     launches = fl.launch_count() - launches_before
     barrier()
     ms = max_over_ranks(ms)
     status = fl.consume_status()
     assert status == 0, f"kernel status {status:#x}"
-    flops_per_step = sum(2.0 * M * N_TOKENS * K for _, M, K, _ in OPT66B_LAYER)
+    flops_per_step = sum(2.0 * M * N_TOKENS * K for _, M, K, _, _ in OPT66B_LAYER)
     value = flops_per_step * args.steps / (ms * 1e-3) / 1e12
 
     # ---- end to end: host activations in, host results out, every step
@@ -316,7 +329,7 @@ def run_reference_gpu(args) -> None:
         return
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    layer = Layer(fl, 0, 1, dev)
+    layer = Layer(fl, 0, 1, dev, reference_splits=True)
     stream = torch.cuda.current_stream(dev).cuda_stream
 
     def step():
@@ -328,7 +341,7 @@ def run_reference_gpu(args) -> None:
     for _ in range(max(args.warmup, 3)):
         step()
     ms = time_loop(step, args.steps, dev)
-    flops_per_step = sum(2.0 * M * N_TOKENS * K for _, M, K, _ in OPT66B_LAYER)
+    flops_per_step = sum(2.0 * M * N_TOKENS * K for _, M, K, _, _ in OPT66B_LAYER)
     per_shape = {}
     for it in layer.items:
         def one(it=it):
@@ -346,7 +359,7 @@ def run_reference_gpu(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -152,7 +152,7 @@ def encode_on_device(stream: int, A_d: int, M: int, K: int, alloc_i32, alloc_u32
 
 
 PLAN_FIELDS = ("cluster_k", "workspace_k", "a_stages", "b_stages", "b_batch", "ring_slots", "chunk_vectors",
-               "scatter_groups", "warps_per_group", "producers")
+               "scatter_warps", "producers")
 
 
 def set_plan(**fields: int) -> None:

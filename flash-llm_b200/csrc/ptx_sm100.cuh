@@ -39,6 +39,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// Arrival that counts as `count` pending arrivals at once.
+__device__ __forceinline__ void mbar_arrive_count(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -157,6 +163,54 @@ umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, u
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// One 128x64 tile of A times one [N x 64] slab of B: the four K=16 MMAs, the commit that hands the A stage back, an
+// optional second commit (B batch finished), and -- issued first so that its shared-memory round trip overlaps the
+// MMA issue -- a probe of the barriers the NEXT tile needs.  All in one asm block because the probe's predicate must
+// survive until after the MMAs, which separate asm statements cannot express.  Returns whether the next tile's
+// barriers had completed at probe time.
+__device__ __forceinline__ bool umma_tile_commit_probe(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                       uint32_t accumulate_first, uint32_t commit_a_bar,
+                                                       uint32_t commit_b_bar, uint32_t do_commit_b,
+                                                       uint32_t next_a_bar, uint32_t next_a_par, uint32_t next_b_bar,
+                                                       uint32_t next_b_par, uint32_t probe_a, uint32_t probe_b)
+{
+    uint32_t ready;
+    asm volatile(
+        "{\n"
+        ".reg .pred pacc, ptrue, pna, pnb, pda, pdb, pcb;\n"
+        ".reg .b64 da, db;\n"
+        "setp.ne.b32 pacc, %5, 0;\n"
+        "setp.eq.b32 ptrue, 0, 0;\n"
+        "setp.ne.b32 pda, %13, 0;\n"
+        "setp.ne.b32 pdb, %14, 0;\n"
+        "setp.ne.b32 pcb, %8, 0;\n"
+        "setp.eq.b32 pna, 0, 0;\n"
+        "setp.eq.b32 pnb, 0, 0;\n"
+        "@pda mbarrier.test_wait.parity.shared::cta.b64 pna, [%9], %10;\n"
+        "@pdb mbarrier.test_wait.parity.shared::cta.b64 pnb, [%11], %12;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %3, %4, pacc;\n"
+        "add.s64 da, %2, 2;\n"
+        "add.s64 db, %3, 2;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %4, ptrue;\n"
+        "add.s64 da, %2, 4;\n"
+        "add.s64 db, %3, 4;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %4, ptrue;\n"
+        "add.s64 da, %2, 6;\n"
+        "add.s64 db, %3, 6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %4, ptrue;\n"
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n"
+        "@pcb tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n"
+        "and.pred pna, pna, pnb;\n"
+        "selp.u32 %0, 1, 0, pna;\n"
+        "}\n"
+        : "=r"(ready)
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(commit_a_bar), "r"(commit_b_bar),
+          "r"(do_commit_b), "r"(next_a_bar), "r"(next_a_par), "r"(next_b_bar), "r"(next_b_par), "r"(probe_a),
+          "r"(probe_b)
+        : "memory");
+    return ready != 0;
 }
 
 // Arrives once on the mbarrier when every tcgen05 operation issued so far by this thread has completed.

@@ -45,29 +45,16 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 static EncodeTiledFn  g_encode_tiled = nullptr;
 static std::once_flag g_encode_once;
 
-template<int N_TILE, int GW>
-static cudaError_t raise_smem_limit_one(int optin)
-{
-    cudaFuncAttributes attr{};
-    cudaError_t        e = cudaFuncGetAttributes(&attr, spmm_tcgen05_kernel<N_TILE, GW>);
-    if (e != cudaSuccess)
-        return e;
-    // the opt-in limit covers static and dynamic shared memory together
-    return cudaFuncSetAttribute(spmm_tcgen05_kernel<N_TILE, GW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                optin - static_cast<int>(attr.sharedSizeBytes));
-}
-
 template<int N_TILE>
 static cudaError_t raise_smem_limit(int optin)
 {
-    cudaError_t e = raise_smem_limit_one<N_TILE, 1>(optin);
-    if (e == cudaSuccess)
-        e = raise_smem_limit_one<N_TILE, 2>(optin);
-    if (e == cudaSuccess)
-        e = raise_smem_limit_one<N_TILE, 4>(optin);
-    if (e == cudaSuccess)
-        e = raise_smem_limit_one<N_TILE, 8>(optin);
-    return e;
+    cudaFuncAttributes attr{};
+    cudaError_t        e = cudaFuncGetAttributes(&attr, spmm_tcgen05_kernel<N_TILE>);
+    if (e != cudaSuccess)
+        return e;
+    // the opt-in limit covers static and dynamic shared memory together
+    return cudaFuncSetAttribute(spmm_tcgen05_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                optin - static_cast<int>(attr.sharedSizeBytes));
 }
 
 static DeviceState* device_state(cudaError_t* err)
@@ -168,28 +155,48 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     const int ctas_flat = tile_rows * n_tiles;
     const int slab      = pl.n_tile * kTileK * 2;
 
-    pl.scatter_groups  = ov.v[kPlanScatterGroups] ? ov.v[kPlanScatterGroups] : 4;
-    pl.warps_per_group = ov.v[kPlanWarpsPerGroup] ? ov.v[kPlanWarpsPerGroup] : 2;
-    pl.producers       = ov.v[kPlanProducers] ? ov.v[kPlanProducers] : 2;
+    // Two pipelines per SM (4 scatter warps, 4 stages each) where they fit; wide-N tiles need the shared memory for
+    // their B batches, so they run one deeper pipeline per SM instead.
+    const bool two_per_sm = pl.n_tile <= 32;
+    pl.scatter_warps   = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps] : (two_per_sm ? 4 : 8);
+    pl.producers       = ov.v[kPlanProducers] ? ov.v[kPlanProducers] : 1;
     pl.chunk_vectors   = ov.v[kPlanChunkVectors] ? ov.v[kPlanChunkVectors] : 512;
-    pl.ring_slots      = ov.v[kPlanRingSlots] ? ov.v[kPlanRingSlots] : (kMaxTileVectors / pl.chunk_vectors + 1);
+    pl.ring_slots      = ov.v[kPlanRingSlots] ? ov.v[kPlanRingSlots]
+                                              : (two_per_sm ? kMaxTileVectors / pl.chunk_vectors + 1 : 8);
     if (!ov.v[kPlanRingSlots])
         pl.ring_slots = (pl.ring_slots + pl.producers - 1) / pl.producers * pl.producers;
-    pl.a_stages        = ov.v[kPlanAStages] ? ov.v[kPlanAStages] : (pl.scatter_groups > 3 ? pl.scatter_groups : 3);
+    pl.a_stages        = ov.v[kPlanAStages] ? ov.v[kPlanAStages] : pl.scatter_warps;
     pl.b_batch         = ov.v[kPlanBBatch] ? ov.v[kPlanBBatch] : (4096 / slab > 0 ? 4096 / slab : 1);
-    pl.b_stages        = ov.v[kPlanBStages] ? ov.v[kPlanBStages] : 3;
+    pl.b_stages        = ov.v[kPlanBStages] ? ov.v[kPlanBStages] : 2;
 
-    // Enough CTAs for two per SM, but never more K parts than K tiles.
-    const int target = st->sm_count * 2;
-    int       want   = (target + ctas_flat - 1) / ctas_flat;
-    if (want < 1)
-        want = 1;
-    if (want > k_tiles)
-        want = k_tiles;
-    pl.cluster_k = ov.v[kPlanClusterK] ? ov.v[kPlanClusterK] : (want < kMaxClusterK ? want : kMaxClusterK);
+    // How to cut K.  A CTA that owns a whole tile row needs no reduction and pays its pipeline fill once, so K is
+    // split only when the tile rows alone leave most CTA slots empty.  Parts that go through the caller's workspace
+    // (fp32 partial matrices, summed by a second kernel; at most Split_K/2 of them) measured cheaper than parts of a
+    // thread-block cluster (summed through distributed shared memory), whose CTAs must be co-scheduled; clusters
+    // take what the workspace cannot.  Replaces the reference's hand-tuned Split_K tables
+    // (kernel_benchmark/benchmark.sh:13-15).
+    const int slots     = st->sm_count * (two_per_sm ? 2 : 1);
+    const int max_extra = ((static_cast<long long>(M) * N) % 4 != 0) ? 1 : (Split_K / 2 > 1 ? Split_K / 2 : 1);
+    int       best_s = 1, best_g = 1;
+    if (ctas_flat * 10 < slots * 6) {
+        int want = (slots + ctas_flat / 2) / ctas_flat;
+        if (want < 1)
+            want = 1;
+        if (want > k_tiles)
+            want = k_tiles;
+        best_g = want < max_extra ? want : max_extra;
+        if (best_g > 8)
+            best_g = 8;
+        best_s = (want + best_g / 2) / best_g;
+        if (best_s < 1)
+            best_s = 1;
+        if (best_s > kMaxClusterK)
+            best_s = kMaxClusterK;
+    }
+    pl.cluster_k = ov.v[kPlanClusterK] ? ov.v[kPlanClusterK] : best_s;
     if (pl.cluster_k > k_tiles)
         pl.cluster_k = k_tiles;
-    int extra = ov.v[kPlanWorkspaceK] ? ov.v[kPlanWorkspaceK] : (want + pl.cluster_k - 1) / pl.cluster_k;
+    int extra = ov.v[kPlanWorkspaceK] ? ov.v[kPlanWorkspaceK] : best_g;
     if (extra > Split_K / 2)
         extra = Split_K / 2;  // the workspace is promised to hold Split_K fp16 matrices = Split_K/2 fp32 partials
     if (extra * pl.cluster_k > k_tiles)
@@ -204,15 +211,12 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
     pl.smem_bytes     = plan_smem_bytes(pl);
 
-    const int  scatter_warps = pl.scatter_groups * pl.warps_per_group;
-    const bool ok = (scatter_warps == 4 || scatter_warps == 8) && pl.scatter_groups >= 1
-                    && (pl.warps_per_group == 1 || pl.warps_per_group == 2 || pl.warps_per_group == 4
-                        || pl.warps_per_group == 8)
+    const bool ok = pl.scatter_warps >= 4 && pl.scatter_warps <= kMaxScatterWarps
                     && pl.producers >= 1 && pl.producers <= kMaxProducers && is_pow2(pl.chunk_vectors)
                     && pl.chunk_vectors >= 64 && pl.ring_slots <= kMaxRingSlots
                     // a slot is always refilled by the same producer warp, and a stage's successive tiles are taken by
                     // groups that cannot be two uses ahead: both keep every mbarrier parity wait within one phase
-                    && pl.ring_slots % pl.producers == 0 && pl.a_stages >= pl.scatter_groups
+                    && pl.ring_slots % pl.producers == 0 && pl.a_stages >= pl.scatter_warps
                     && pl.ring_slots * pl.chunk_vectors >= kMaxTileVectors + pl.chunk_vectors
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
@@ -233,7 +237,7 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cudaLaunchConfig_t  cfg{};
     cudaLaunchAttribute attr[1];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
-    cfg.blockDim         = dim3((pl.producers + 2 + pl.scatter_groups * pl.warps_per_group) * 32, 1, 1);
+    cfg.blockDim         = dim3((pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream           = stream;
     attr[0].id               = cudaLaunchAttributeClusterDimension;
@@ -243,12 +247,7 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cfg.attrs                = attr;
     cfg.numAttrs             = 1;
     count_launch();
-    switch (pl.warps_per_group) {
-        case 1: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 1>, tmap, params);
-        case 2: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 2>, tmap, params);
-        case 4: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 4>, tmap, params);
-        default: return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE, 8>, tmap, params);
-    }
+    return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
 }
 
 static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws, long long count, int parts)
@@ -415,9 +414,8 @@ int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count)
     SpmmPlan pl{};
     if ((err = make_plan(st, M, N, K, Split_K, &pl)) != cudaSuccess)
         return static_cast<int>(err);
-    const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k,   pl.a_stages,       pl.b_stages,
-                                             pl.b_batch,    pl.ring_slots,    pl.chunk_vectors,  pl.scatter_groups,
-                                             pl.warps_per_group, pl.producers, pl.smem_bytes};
+    const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k, pl.a_stages,      pl.b_stages,   pl.b_batch,
+                                             pl.ring_slots, pl.chunk_vectors, pl.scatter_warps, pl.producers,  pl.smem_bytes};
     for (int i = 0; i < count && i <= kPlanFieldCount; ++i)
         out[i] = values[i];
     return 0;

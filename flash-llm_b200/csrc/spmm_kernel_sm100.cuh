@@ -45,7 +45,7 @@ constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
 
 // Pipeline-analysis builds (never the shipped one) drop one stage of the kernel to see what it costs, as the
 // reference does with its own stubs (csrc/SpMM_Kernel.cuh:64-111).  Bits: 1 no zero-fill, 2 no scatter stores,
-// 4 no MMA, 8 no ring reads, 16 no scatter-group barrier, 32 no B loads.  Results are wrong with any bit set.
+// 8 no ring reads.  Results are wrong with any bit set.
 #ifndef FLASHLLM_ABLATE
 #define FLASHLLM_ABLATE 0
 #endif
@@ -195,25 +195,31 @@ __device__ __forceinline__ void scatter_vector(uint32_t stage, const uint4& w)
     scatter_word(stage, w.w);
 }
 
-// Zeroes one 16 KB stage with the GW*32 threads of a scatter group, fully unrolled: 32 / 16 / 8 stores per thread.
-template<int GW>
-__device__ __forceinline__ void zero_fill_stage(uint32_t stage, int gtid)
+// Zeroes one 16 KB stage with the 32 lanes of a scatter warp, fully unrolled: 32 stores of 16 bytes per lane.
+__device__ __forceinline__ void zero_fill_stage(uint32_t stage, int lane)
 {
-    constexpr int kPerThread = kDenseTileBytes / (GW * 32 * 16);
+#ifdef FLASHLLM_ZERO_BULK
+    // one bulk zero-initialising store per lane group instead of per-lane vector stores
+    if (lane < FLASHLLM_ZERO_BULK)
+        asm volatile("st.bulk.weak.shared::cta [%0], %1, 0;" ::"r"(stage + lane * (kDenseTileBytes / FLASHLLM_ZERO_BULK)),
+                     "l"(static_cast<unsigned long long>(kDenseTileBytes / FLASHLLM_ZERO_BULK))
+                     : "memory");
+    return;
+#endif
 #pragma unroll
-    for (int q = 0; q < kPerThread; ++q)
-        sts_zero16(stage + static_cast<uint32_t>(q * GW * 32 + gtid) * 16u);
+    for (int q = 0; q < kDenseTileBytes / (32 * 16); ++q)
+        sts_zero16(stage + static_cast<uint32_t>(q * 32 + lane) * 16u);
 }
 
-// N_TILE: MMA N (tokens per CTA).  GW: warps per scatter group (compile-time so that the per-tile code is straight
-// line: the per-tile paths are latency-bound chains of a few dozen instructions, and every loop-carried branch or
-// runtime division in them costs more than the work it guards).
-template<int N_TILE, int GW>
+// N_TILE: MMA N (tokens per CTA).  The per-tile paths of every role are latency-bound chains of a few dozen
+// instructions: each shared-memory or mbarrier round trip in them costs 30-150 cycles and nothing else runs in that
+// thread meanwhile.  Hence straight-line code, probes issued side by side or ahead of time, no runtime divisions,
+// and no cross-warp hand-offs other than the mbarriers themselves.
+template<int N_TILE>
 __global__ void __launch_bounds__(kMaxThreads, 1)
     spmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_b, const SpmmParams p)
 {
     static_assert(N_TILE == 16 || N_TILE == 32 || N_TILE == 64 || N_TILE == 128, "unsupported MMA N");
-    static_assert(GW == 1 || GW == 2 || GW == 4 || GW == 8, "unsupported scatter group size");
     constexpr uint32_t kBSlab    = N_TILE * kTileK * 2;  // one K tile of B in shared memory
     constexpr uint32_t kTmemCols = N_TILE < 32 ? 32 : N_TILE;
 
@@ -239,8 +245,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     const int       S          = plan.cluster_k;
     const int       G          = plan.workspace_k;
     const int       P          = plan.producers;
-    const int       NG         = plan.scatter_groups;
-    const int       NSW        = NG * GW;
+    const int       NSW        = plan.scatter_warps;  // each scatter warp decompresses whole tiles on its own
     const int       NTS        = NSW * 32;
     const int       b_warp     = P;      // warp that loads B
     const int       mma_warp   = P + 1;  // warp that issues MMAs and owns TMEM
@@ -292,10 +297,12 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         const unsigned int status_now = *reinterpret_cast<volatile unsigned int*>(p.status);
         for (int i = 0; i < ring_slots; ++i) {
             ptx::mbar_init(ring_full + 8u * i, 1);
-            ptx::mbar_init(ring_empty + 8u * i, 1);
+            // a slot is free again once every one of its CV vectors has been consumed: the warps that consume them
+            // arrive with the number of vectors they took, in whatever order the tiles finish
+            ptx::mbar_init(ring_empty + 8u * i, CV);
         }
         for (int i = 0; i < a_stages; ++i) {
-            ptx::mbar_init(a_full + 8u * i, GW);
+            ptx::mbar_init(a_full + 8u * i, 1);
             ptx::mbar_init(a_empty + 8u * i, 1);
         }
         for (int i = 0; i < b_stages; ++i) {
@@ -365,18 +372,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         }
     }
     else if (warp == b_warp) {
-#ifdef FLASHLLM_TRACE
-        if (lane == 1 && L > 0) {  // timeline builds: a monitor thread timestamps the landing of every chunk
-            const int nvec_m    = offs[L] - offs[0];
-            const int nchunks_m = (nvec_m + CV - 1) >> cv_shift;
-            for (int c = 0; c < nchunks_m && c < FL_TRACE_BASE + kTraceDepth; ++c) {
-                if (!wait_bounded(ring_full + 8u * (c % ring_slots), static_cast<uint32_t>(c / ring_slots) & 1u,
-                                  abort_flag, p.status))
-                    break;
-                FL_TRACE(13, c);
-            }
-        }
-#endif
         // ================================================================ B loader: KB K tiles per TMA instruction
         if (lane == 0 && L > 0 && !(FLASHLLM_ABLATE & 32)) {
             const int batches = (L + KB - 1) / KB;
@@ -407,105 +402,80 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         }
     }
     else if (warp == mma_warp) {
-        // ================================================================ MMA issuer (tile order) + ring release
-        // The whole warp takes part in the waiting so that the barriers a tile needs are probed side by side (a probe
-        // is a shared-memory round trip of a hundred cycles or more; one after another they would pace the kernel).
-        // Lane 0 then issues the MMAs, commits, and hands ring chunks back.
-        if (L > 0) {
+        // ================================================================ MMA issuer (tile order)
+        // Per tile: four MMAs, the commit that hands the stage back, and a probe of the next tile's barriers issued
+        // ahead of the MMAs so that its round trip is hidden behind them.
+        if (lane == 0 && L > 0) {
             const uint32_t idesc   = ptx::umma_idesc_f16_f32(kTileM, N_TILE);
-            const int      v_first = offs[0];
-            // Descriptors differ only in the 16-byte-unit start address (low bits): build them once, then add.
             const uint64_t a_desc0 = ptx::umma_desc_kmajor_sw128(a_base);
             const uint64_t b_desc0 = ptx::umma_desc_kmajor_sw128(b_base);
             int            s = 0, bs = 0, kb = 0;
             uint32_t       a_par = 0, b_par = 0;
-            int            released = 0, rel_slot = 0;
-            int            tile_end = offs[1];  // fetched one tile ahead of its use
-            bool           alive    = true;
-            for (int j = 0; j < L && alive; ++j) {
+            bool           ready = false;
+            for (int j = 0; j < L; ++j) {
                 FL_TRACE(7, j);
-                // lane 0 watches the decompressed tile, lane 1 the B batch (when this tile opens one)
-                const uint32_t my_bar = lane == 0 ? a_full + 8u * s : b_full + 8u * bs;
-                const uint32_t my_par = lane == 0 ? a_par : b_par;
-                const bool     mine   = lane == 0 || (lane == 1 && kb == 0 && !(FLASHLLM_ABLATE & 32));
-                bool           ready  = !mine || ptx::mbar_test_wait(my_bar, my_par);
-                if (!__all_sync(0xFFFFFFFFu, ready)) {
-                    if (mine && !ready)
-                        ready = wait_bounded(my_bar, my_par, abort_flag, p.status);
-                    if (!__all_sync(0xFFFFFFFFu, ready))
+                if (!ready) {
+                    if (!wait_bounded(a_full + 8u * s, a_par, abort_flag, p.status))
+                        break;
+                    if (kb == 0 && !wait_bounded(b_full + 8u * bs, b_par, abort_flag, p.status))
                         break;
                 }
                 FL_TRACE(9, j);
-                const int next_end = (j + 2 <= L) ? offs[j + 2] : 0;  // in flight during the MMA issue
-                if (lane == 0) {
-                    ptx::tc_fence_after_sync();
-                    const uint64_t a_desc = a_desc0 + static_cast<uint32_t>(s * (kDenseTileBytes >> 4));
-                    const uint64_t b_desc = b_desc0 + static_cast<uint32_t>((bs * KB + kb) * (kBSlab >> 4));
-#pragma unroll
-                    for (int kk = 0; kk < ((FLASHLLM_ABLATE & 4) ? 0 : kTileK / kUmmaK); ++kk) {
-                        ptx::umma_f16_ss(tmem_acc, a_desc + kk * (kUmmaK * 2 >> 4), b_desc + kk * (kUmmaK * 2 >> 4), idesc,
-                                         (j | kk) != 0 ? 1u : 0u);
-                    }
-                    FL_TRACE(18, j);
-                    ptx::umma_commit(a_empty + 8u * s);
-                    if (kb + 1 == KB || j == L - 1)
-                        ptx::umma_commit(b_empty + 8u * bs);
-                    FL_TRACE(10, j);
-                    // Tile j is decompressed: ring chunks that end at or before its last vector are free again.
-                    const int done = (tile_end - v_first) >> cv_shift;
-                    while (released < done) {
-                        FL_TRACE(14, released);
-                        ptx::mbar_arrive(ring_empty + 8u * rel_slot);
-                        ++released;
-                        if (++rel_slot == ring_slots)
-                            rel_slot = 0;
-                    }
-                    *tiles_scattered = j + 1;
-                    FL_TRACE(19, j);
+                int      s_n = s + 1, kb_n = kb + 1, bs_n = bs;
+                uint32_t a_par_n = a_par, b_par_n = b_par;
+                if (s_n == a_stages) {
+                    s_n = 0;
+                    a_par_n ^= 1u;
                 }
-                tile_end = next_end;
-                if (++s == a_stages) {
-                    s = 0;
-                    a_par ^= 1u;
-                }
-                if (++kb == KB) {
-                    kb = 0;
-                    if (++bs == b_stages) {
-                        bs = 0;
-                        b_par ^= 1u;
+                if (kb_n == KB) {
+                    kb_n = 0;
+                    if (++bs_n == b_stages) {
+                        bs_n = 0;
+                        b_par_n ^= 1u;
                     }
                 }
+                const bool has_next = j + 1 < L;
+                ptx::tc_fence_after_sync();
+                ready = ptx::umma_tile_commit_probe(
+                    tmem_acc, a_desc0 + static_cast<uint32_t>(s * (kDenseTileBytes >> 4)),
+                    b_desc0 + static_cast<uint32_t>((bs * KB + kb) * (kBSlab >> 4)), idesc, j != 0 ? 1u : 0u, a_empty + 8u * s,
+                    b_empty + 8u * bs, (kb_n == 0 || !has_next) ? 1u : 0u, a_full + 8u * s_n, a_par_n, b_full + 8u * bs_n, b_par_n,
+                    has_next ? 1u : 0u, (has_next && kb_n == 0) ? 1u : 0u);
+                FL_TRACE(10, j);
+                *tiles_scattered = j + 1;
+                s     = s_n;
+                kb    = kb_n;
+                bs    = bs_n;
+                a_par = a_par_n;
+                b_par = b_par_n;
+                FL_TRACE(19, j);
             }
-            if (lane == 0)
-                ptx::umma_commit(acc_full);
+            ptx::umma_commit(acc_full);
         }
     }
     else {
-        // ================================================================ scatter groups: one whole tile at a time
-        const int     sw   = warp - first_sw;  // scatter warp index
-        const int     grp  = sw / GW;
-        const int     gtid = (sw % GW) * 32 + lane;
-        constexpr int GT   = GW * 32;
+        // ================================================================ scatter warps: one whole tile at a time
+        const int sw = warp - first_sw;  // scatter warp index
         if (L > 0) {
             const int v_first = offs[0];
             // Stage and ring-slot indices advance by repeated subtraction: a runtime division costs the warp more than
             // a hundred cycles of dependent latency, several times per tile.
-            int      s        = grp % a_stages;  // stage of tile j
-            uint32_t a_use    = static_cast<uint32_t>(grp / a_stages);
-            int      cur_c    = 0;               // a chunk index at or before this tile's first chunk ...
-            int      cur_slot = 0;               // ... and its ring slot and use count
+            int      s        = sw % a_stages;  // stage of tile j
+            uint32_t a_use    = static_cast<uint32_t>(sw / a_stages);
+            int      cur_c    = 0;              // a chunk index at or before this tile's first chunk ...
+            int      cur_slot = 0;              // ... and its ring slot and use count
             uint32_t cur_use  = 0;
-            int      vb_next  = grp < L ? offs[grp] - v_first : 0;  // offsets are fetched one tile ahead of their use
-            int      ve_next  = grp < L ? offs[grp + 1] - v_first : 0;
-            for (int j = grp; j < L; j += NG, s += NG) {
-                if (s >= a_stages) {  // a_stages >= NG: one step is enough
+            int      vb_next  = sw < L ? offs[sw] - v_first : 0;  // offsets are fetched one tile ahead of their use
+            int      ve_next  = sw < L ? offs[sw + 1] - v_first : 0;
+            for (int j = sw; j < L; j += NSW, s += NSW) {
+                if (s >= a_stages) {  // a_stages >= NSW: one step is enough
                     s -= a_stages;
                     ++a_use;
                 }
                 const int vb = vb_next, ve = ve_next;
-                if (j + NG < L) {
-                    vb_next = offs[j + NG] - v_first;
-                    ve_next = offs[j + NG + 1] - v_first;
+                if (j + NSW < L) {
+                    vb_next = offs[j + NSW] - v_first;
+                    ve_next = offs[j + NSW + 1] - v_first;
                 }
                 // end of the newest tile whose MMA must have finished before this stage was handed back to us
                 const int      settled = j >= a_stages ? offs[j - a_stages + 1] - v_first : 0;
@@ -513,9 +483,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                 const bool     bad     = (ve < vb) || (ve - vb > kMaxTileVectors) || (vb < 0);
                 if (bad)
                     atomicOr(p.status, kStatusBadTileOffsets);
-                if (gtid == 0)
+                if (lane == 0)
                     FL_TRACE(0, j);
-                // ---- everything this tile waits for, probed side by side: lane 0 the stage, lanes 1.. the ring chunks
                 const int c_first = vb >> cv_shift;
                 const int n_chunk = ve > vb ? (((ve - 1) >> cv_shift) - c_first + 1) : 0;
                 while (cur_c < c_first) {
@@ -532,7 +501,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                 const int c_last = c_first + n_chunk - 1;
                 if (ok && n_chunk > 0 && c_last >= ring_slots && ((c_last - ring_slots + 1) << cv_shift) > settled) {
                     if (lane == 0) {
-                        int need = j;  // first tile index whose completion covers the previous occupant
+                        int need = j;  // last tile that overlaps the previous occupant
                         while (need > 0 && offs[need] - v_first >= ((c_last - ring_slots + 1) << cv_shift))
                             --need;
                         uint64_t t0 = 0;
@@ -556,6 +525,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                     }
                     ok = __shfl_sync(0xFFFFFFFFu, ok ? 1u : 0u, 0) != 0;
                 }
+                // ---- everything this tile waits for, probed side by side: lane 0 the stage, lanes 1.. the ring chunks
+                uint32_t my_slot_bar = 0;  // lanes 1..n_chunk: byte offset of their chunk's barrier pair
+                uint32_t my_count    = 0;  // ... and the number of this tile's vectors inside that chunk
                 if (ok) {
                     uint32_t my_bar, my_par;
                     bool     mine;
@@ -571,9 +543,16 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                             slot -= ring_slots;
                             ++use;
                         }
-                        my_bar = ring_full + 8u * slot;
-                        my_par = use & 1u;
-                        mine   = lane - 1 < n_chunk;
+                        my_slot_bar = 8u * slot;
+                        my_bar      = ring_full + my_slot_bar;
+                        my_par      = use & 1u;
+                        mine        = lane - 1 < n_chunk;
+                        if (mine) {
+                            const int c  = c_first + lane - 1;
+                            const int lo = vb > (c << cv_shift) ? vb : (c << cv_shift);
+                            const int hi = ve < ((c + 1) << cv_shift) ? ve : ((c + 1) << cv_shift);
+                            my_count     = static_cast<uint32_t>(hi - lo);
+                        }
                     }
                     bool ready = !mine || ptx::mbar_test_wait(my_bar, my_par);
                     if (!__all_sync(0xFFFFFFFFu, ready)) {
@@ -582,44 +561,32 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                         ok = __all_sync(0xFFFFFFFFu, ready);
                     }
                 }
-                if (gtid == 0)
+                if (lane == 0)
                     FL_TRACE(3, j);
                 if (ok && !(FLASHLLM_ABLATE & 1))
-                    zero_fill_stage<GW>(stage, gtid);
-                if (gtid == 0)
+                    zero_fill_stage(stage, lane);
+                if (lane == 0)
                     FL_TRACE(2, j);
-                // Zeroes must be in place before any warp of the group scatters; the same barrier makes giving up
-                // unanimous inside the group.
-                bool give_up = !ok;
-#if (FLASHLLM_ABLATE & 16)
-                give_up = __any_sync(0xFFFFFFFFu, give_up);
-#else
-                if (GW == 1)
-                    give_up = __any_sync(0xFFFFFFFFu, give_up);  // also orders the zero stores before the scatter
-                else
-                    give_up = barrier_any(1 + grp, GT, give_up);
-#endif
-                if (give_up) {
+                // the warp barrier orders the zero stores before the scatter stores of other lanes
+                if (__any_sync(0xFFFFFFFFu, !ok)) {
                     if (bad)
                         *abort_flag = 1u;
                     break;
                 }
-                if (gtid == 0)
-                    FL_TRACE(4, j);
 #if !(FLASHLLM_ABLATE & 8)
-                int      v   = vb + gtid;
-                uint32_t pos = (static_cast<uint32_t>(cur_slot) << cv_shift) + (static_cast<uint32_t>(vb) & (CV - 1)) + gtid;
+                int      v   = vb + lane;
+                uint32_t pos = (static_cast<uint32_t>(cur_slot) << cv_shift) + (static_cast<uint32_t>(vb) & (CV - 1)) + lane;
                 if (pos >= ring_vecs)
-                    pos -= ring_vecs;  // GT <= CV <= ring_vecs: one step is enough
+                    pos -= ring_vecs;
                 // four vectors per trip: the loads are issued together, then their sixteen stores
-                for (; v + 3 * GT < ve; v += 4 * GT) {
-                    uint32_t p1 = pos + GT;
+                for (; v + 96 < ve; v += 128) {
+                    uint32_t p1 = pos + 32;
                     if (p1 >= ring_vecs)
                         p1 -= ring_vecs;
-                    uint32_t p2 = p1 + GT;
+                    uint32_t p2 = p1 + 32;
                     if (p2 >= ring_vecs)
                         p2 -= ring_vecs;
-                    uint32_t p3 = p2 + GT;
+                    uint32_t p3 = p2 + 32;
                     if (p3 >= ring_vecs)
                         p3 -= ring_vecs;
                     const uint4 w0 = lds16(ring_base + pos * 16u);
@@ -635,11 +602,11 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                     scatter_vector(stage, w2);
                     scatter_vector(stage, w3);
 #endif
-                    pos = p3 + GT;
+                    pos = p3 + 32;
                     if (pos >= ring_vecs)
                         pos -= ring_vecs;
                 }
-                for (; v < ve; v += GT) {
+                for (; v < ve; v += 32) {
                     const uint4 w0 = lds16(ring_base + pos * 16u);
 #if (FLASHLLM_ABLATE & 2)
                     if ((w0.x ^ w0.y ^ w0.z ^ w0.w) == 0x9E3779B9u)
@@ -647,18 +614,21 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 #else
                     scatter_vector(stage, w0);
 #endif
-                    pos += GT;
+                    pos += 32;
                     if (pos >= ring_vecs)
                         pos -= ring_vecs;
                 }
 #endif
-                if (gtid == 0)
+                if (lane == 0)
                     FL_TRACE(5, j);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
+                // lane 0 publishes the tile; the lanes that watched a ring chunk hand its vectors back
                 if (lane == 0)
                     ptx::mbar_arrive(a_full + 8u * s);
-                if (gtid == 0)
+                else if (my_count != 0)
+                    ptx::mbar_arrive_count(ring_empty + my_slot_bar, my_count);
+                if (lane == 0)
                     FL_TRACE(6, j);
             }
         }
@@ -670,10 +640,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         acc_ok = __all_sync(0xFFFFFFFFu, acc_ok && (*abort_flag == 0u));
         ptx::tc_fence_after_sync();
 
-        const int quarter     = warp & 3;  // TMEM lanes this warp may read: 32*quarter ..
-        const int per_quarter = NSW / 4;   // warps sharing a lane quarter split the columns
+        const int quarter     = warp & 3;    // TMEM lanes this warp may read: 32*quarter ..
+        const int per_quarter = NSW / 4;     // warps sharing a lane quarter split the columns (NSW >= 4)
         const int col_share   = (N_TILE / per_quarter) < 8 ? 8 : (N_TILE / per_quarter);
-        const int col_begin   = (sw / 4) * col_share;
+        const int col_begin   = sw < per_quarter * 4 ? (sw / 4) * col_share : N_TILE;  // warps past a multiple of 4 idle
         const int col_end     = (col_begin + col_share) < N_TILE ? (col_begin + col_share) : N_TILE;
         const int n_valid     = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
         const int row_in_tile = quarter * 32 + lane;

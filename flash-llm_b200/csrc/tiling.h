@@ -19,7 +19,7 @@ constexpr int kMaxBStages      = 8;
 constexpr int kMaxRingSlots    = 64;
 constexpr int kMaxClusterK     = 8;   // portable cluster size limit
 constexpr int kMaxProducers    = 4;   // warps issuing bulk copies of the compressed stream
-constexpr int kMaxScatterWarps = 8;
+constexpr int kMaxScatterWarps = 12;
 // warps: [0, producers) copy producers, then one B-tile loader, then the MMA issuer / TMEM owner, then scatter warps
 constexpr int kMaxThreads = (kMaxProducers + 2 + kMaxScatterWarps) * 32;
 
@@ -37,8 +37,7 @@ enum PlanField {
     kPlanBBatch,          // K tiles of B fetched by one TMA instruction
     kPlanRingSlots,       // compressed-stream ring: slots ...
     kPlanChunkVectors,    // ... of this many 16-byte vectors (power of two)
-    kPlanScatterGroups,   // groups of scatter warps; each group decompresses whole tiles on its own
-    kPlanWarpsPerGroup,   // warps in a scatter group
+    kPlanScatterWarps,    // warps that decompress tiles, one whole tile per warp at a time (4..12, <= a_stages)
     kPlanProducers,       // warps issuing the bulk copies
     kPlanFieldCount
 };
@@ -52,8 +51,7 @@ struct SpmmPlan {
     int b_batch;
     int ring_slots;
     int chunk_vectors;
-    int scatter_groups;
-    int warps_per_group;
+    int scatter_warps;
     int producers;
     int offsets_staged;  // TileOffsets entries a CTA may stage in shared memory (0 = read them from global memory)
     int smem_bytes;      // dynamic shared memory of the launch

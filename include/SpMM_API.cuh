@@ -111,19 +111,19 @@ int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Works
 
 /* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
  * csrc/SpMM_API.cu:79-118): fixes launch-plan fields for subsequent calls from this process.  `fields` holds up to
- * ten ints, 0 = choose automatically, in this order:
+ * nine ints, 0 = choose automatically, in this order:
  *   0 cluster_k       K parts summed inside a thread-block cluster through distributed shared memory (1..8)
  *   1 workspace_k     extra K parts through Reduction_Workspace (capped at Split_K/2 of the call: an fp32 partial
  *                     matrix takes the room of two fp16 ones)
  *   2 a_stages        decompressed 128x64 tiles in flight        3 b_stages  B batches in flight
  *   4 b_batch         K tiles of B per TMA instruction
  *   5 ring_slots x 6 chunk_vectors (16 bytes each, power of two): the compressed-stream ring
- *   7 scatter_groups x 8 warps_per_group: decompression warps (4 or 8 in total)
- *   9 producers       warps issuing the bulk copies (1..4)
+ *   7 scatter_warps   warps that decompress tiles, one whole tile per warp at a time (4..12, at most a_stages)
+ *   8 producers       warps issuing the bulk copies (1..4; must divide ring_slots)
  * FlashLLM_SetPlan(nullptr, 0) restores automatic choice. */
 void FlashLLM_SetPlan(const int* fields, int count);
 
-/* Describes the plan the next SpMM call with these sizes would use: out[0..9] as above, out[10] = dynamic shared
+/* Describes the plan the next SpMM call with these sizes would use: out[0..8] as above, out[9] = dynamic shared
  * memory in bytes; `count` = entries available in `out`. */
 int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count);
 

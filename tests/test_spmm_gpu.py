@@ -69,13 +69,14 @@ def test_workspace_split_k(lib, oracle, split_k, workspace_k, cluster_k):
     _run_case(lib, oracle, 256, 2048, 16, 0.9, split_k=split_k, plan=dict(cluster_k=cluster_k, workspace_k=workspace_k))
 
 
-@pytest.mark.parametrize("plan", [dict(a_stages=1, b_stages=1, b_batch=1, scatter_groups=1, warps_per_group=8), dict(a_stages=2, b_stages=8, b_batch=3, scatter_groups=2, warps_per_group=4),
-                                  dict(a_stages=6, b_stages=2, b_batch=8), dict(scatter_groups=1, warps_per_group=4),
-                                  dict(scatter_groups=2, warps_per_group=4), dict(scatter_groups=8, warps_per_group=1, a_stages=8),
-                                  dict(scatter_groups=2, warps_per_group=2, a_stages=5),
-                                  dict(producers=1), dict(producers=4, chunk_vectors=128, ring_slots=32),
+@pytest.mark.parametrize("plan", [dict(a_stages=4, b_stages=1, b_batch=1), dict(a_stages=5, b_stages=8, b_batch=3),
+                                  dict(a_stages=8, b_stages=2, b_batch=8, scatter_warps=8),
+                                  dict(scatter_warps=6, a_stages=7), dict(scatter_warps=10, a_stages=10, chunk_vectors=256, ring_slots=9),
+                                  dict(scatter_warps=5, a_stages=5),
+                                  dict(producers=1, ring_slots=9), dict(producers=4, chunk_vectors=128, ring_slots=32),
                                   dict(chunk_vectors=128, ring_slots=18, producers=3),
-                                  dict(chunk_vectors=256, ring_slots=10), dict(chunk_vectors=1024, ring_slots=3, a_stages=2, producers=1, scatter_groups=2, warps_per_group=4)])
+                                  dict(chunk_vectors=512, ring_slots=6, producers=2),
+                                  dict(chunk_vectors=1024, ring_slots=3, a_stages=4)])
 def test_pipeline_shapes(lib, oracle, plan):
     _run_case(lib, oracle, 256, 1536, 16, 0.7, plan=dict(cluster_k=2, **plan))
 
