@@ -19,5 +19,6 @@ from .api import (  # noqa: F401
     library,
     set_plan,
     splitk_reduction,
+    spmm_splitk_no_alloc,
 )
 from . import synthetic  # noqa: F401

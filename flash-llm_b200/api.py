@@ -58,6 +58,8 @@ def library() -> C.CDLL:
     L.FlashLLM_EncodeOnDevice_Pack.restype = C.c_int
     L.FlashLLM_EncodeOnDevice_Pack.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                C.c_int]
+    L.FlashLLM_SpMM_SplitK_NoAlloc.restype = C.c_int
+    L.FlashLLM_SpMM_SplitK_NoAlloc.argtypes = [C.c_void_p] * 5 + [C.c_int] * 4
     L.FlashLLM_SplitK_Reduction.restype = C.c_int
     L.FlashLLM_SplitK_Reduction.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
     L.FlashLLM_SetPlan.argtypes = [_i32p, C.c_int]
@@ -131,6 +133,16 @@ def SpMM_SplitK_API(stream: int, A: int | None, Compressed_A: int, TileOffsets: 
     code = library().FlashLLM_SpMM_SplitK(stream, A, Compressed_A, TileOffsets, B, C_out, M, N, K,
                                           Reduction_Workspace, Split_K)
     _check(code, f"SpMM_SplitK_API(M={M}, N={N}, K={K}, Split_K={Split_K})")
+
+
+def spmm_splitk_no_alloc(stream: int, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int, N: int, K: int,
+                         Split_K: int) -> None:
+    """SpMM for callers that may not allocate device memory (graph capture in progress, a fully pre-assigned
+    memory pool, a plug-in that only receives its buffers): the split-K scratch is an 8 MiB array inside the
+    library instead of a caller workspace.  ``Split_K*M*N*2`` must fit in it.  Calls that overlap on the GPU share
+    that array and race; the first call on a device should precede any stream capture."""
+    code = library().FlashLLM_SpMM_SplitK_NoAlloc(stream, Compressed_A, TileOffsets, B, C_out, M, N, K, Split_K)
+    _check(code, f"SpMM_SplitK_NoAlloc(M={M}, N={N}, K={K}, Split_K={Split_K})")
 
 
 def splitk_reduction(stream: int, C_out: int, workspace: int, M: int, N: int, split_k: int) -> None:

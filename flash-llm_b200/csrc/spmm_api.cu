@@ -18,6 +18,13 @@ namespace flashllm {
 
 __device__ unsigned int g_status_word = 0;
 
+// Scratch of the allocation-free entry point FlashLLM_SpMM_SplitK_NoAlloc: room for the fp32 partial matrices the
+// K split parks between the SpMM kernel and its reduction.  It lives in the library image, so every GPU that loads
+// the library carries these 8 MiB until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress; the device address obtained from it (once per device) is what the kernels receive.
+constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
 static std::atomic<unsigned long long> g_launches{0};
 
 void count_launch()
@@ -35,6 +42,7 @@ struct DeviceState {
     int            sm_count   = 0;
     int            smem_optin = 0;
     unsigned int*  status     = nullptr;
+    unsigned char* noalloc_scratch = nullptr;  // device address of g_noalloc_scratch on this device
 };
 
 static DeviceState g_devices[kMaxDevices];
@@ -74,6 +82,8 @@ static DeviceState* device_state(cudaError_t* err)
             e = cudaDeviceGetAttribute(&st->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (e == cudaSuccess)
             e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->status), g_status_word);
+        if (e == cudaSuccess)
+            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->noalloc_scratch), g_noalloc_scratch);
         // The opt-in limit is a per-device property of each kernel; raise it once instead of on every call
         // (the reference calls cudaFuncSetAttribute per launch, csrc/SpMM_API.cu:36-37).
         if (e == cudaSuccess)
@@ -384,6 +394,36 @@ int FlashLLM_SpMM_SplitK(void*       stream,
                                             K,
                                             static_cast<half*>(Reduction_Workspace),
                                             Split_K));
+}
+
+int FlashLLM_SpMM_SplitK_NoAlloc(void*       stream,
+                                 const void* Compressed_A,
+                                 const int*  TileOffsets,
+                                 const void* B,
+                                 void*       C,
+                                 int         M,
+                                 int         N,
+                                 int         K,
+                                 int         Split_K)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || Split_K < 1)
+        return static_cast<int>(cudaErrorInvalidValue);
+    const unsigned long long need = 2ull * static_cast<unsigned long long>(Split_K) * M * N;  // Split_K fp16 matrices
+    if (need > kNoAllocScratchBytes) {
+        fprintf(stderr,
+                "FlashLLM_SpMM_SplitK_NoAlloc: Split_K*M*N*2 = %llu bytes exceeds the built-in %zu-byte scratch; lower "
+                "Split_K (1 needs none) or use FlashLLM_SpMM_SplitK with a workspace of your own.\n",
+                need, kNoAllocScratchBytes);
+        return static_cast<int>(cudaErrorInvalidValue);
+    }
+    cudaError_t  err = cudaSuccess;
+    DeviceState* st  = device_state(&err);  // first call on a device: looks the scratch address up, allocates nothing
+    if (!st)
+        return static_cast<int>(err);
+    return static_cast<int>(SpMM_SplitK_API(static_cast<cudaStream_t>(stream), nullptr,
+                                            static_cast<const uint4*>(Compressed_A), TileOffsets,
+                                            static_cast<const half*>(B), static_cast<half*>(C), M, N, K,
+                                            reinterpret_cast<half*>(st->noalloc_scratch), Split_K));
 }
 
 int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K)

@@ -105,6 +105,32 @@ int FlashLLM_EncodeOnDevice_TileOffsets(void* stream, const void* A_d, int M, in
 int FlashLLM_EncodeOnDevice_Pack(void* stream, const void* A_d, int M, int K, const int* TileOffsets_d,
                                  uint32_t* Compressed_A_d, int reorder);
 
+/* SpMM for callers that must not allocate device memory.  (No counterpart in the reference, whose callers always
+ * bring a Reduction_Workspace of their own.)  Some hosts of this library cannot call cudaMalloc at the point where
+ * they need the product: code running while a CUDA graph is being captured, a serving loop whose memory pool was
+ * handed out in full at start-up, a plug-in that is only given input and output buffers.  This entry point is
+ * SpMM_SplitK_API with the split-K workspace replaced by an 8 MiB scratch array that is part of the library image:
+ * every GPU on which the library is loaded carries it until the process exits.
+ *   - Same arguments and results as FlashLLM_SpMM_SplitK, minus `A` and `Reduction_Workspace`.
+ *   - Split_K*M*N*2 bytes (what a caller-owned workspace would need) must not exceed 8 MiB; larger requests print
+ *     a message to stderr and return cudaErrorInvalidValue.  Split_K = 1 never touches the scratch.
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine.  The first call on each device looks up the
+ *     scratch's device address (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make that first
+ *     call with the device current and before any stream capture begins.
+ *   - All calls on a device share the one scratch array, which keeps the previous call's partial sums; every call
+ *     overwrites the part it reads back, so nothing needs clearing, but two calls that overlap on the GPU (different
+ *     streams, or graphs replayed concurrently) race on it.  Serialise them, or give the second one a workspace of
+ *     its own through FlashLLM_SpMM_SplitK. */
+int FlashLLM_SpMM_SplitK_NoAlloc(void*       stream,
+                                 const void* Compressed_A,
+                                 const int*  TileOffsets,
+                                 const void* B,
+                                 void*       C,
+                                 int         M,
+                                 int         N,
+                                 int         K,
+                                 int         Split_K);
+
 /* Split-K reduction on its own (reference csrc/Reduction_Kernel.cuh:24-45):
  * C[i] = fp16(sum_s float(Workspace[s*M*N + i])). */
 int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K);
