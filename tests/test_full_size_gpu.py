@@ -57,6 +57,9 @@ def test_full_size_row_blocks_and_properties(lib, oracle, M, K, N, sparsity, spl
     # a different K split must agree (cluster sum vs workspace sum vs none)
     other = _spmm(lib, comp, offs, B, M, N, K, 8, plan=dict(cluster_k=2, workspace_k=2)).cpu().numpy()
     assert_close(other, got.astype(np.float32), "K split 2x2 vs automatic")
-    # linearity: SpMM(2 B) == 2 SpMM(B) exactly (powers of two commute with every rounding step)
+    # linearity: SpMM(2 B) == 2 SpMM(B) exactly -- powers of two commute with every rounding step, except where the
+    # fp16 result is subnormal (fixed spacing 2^-24 there), so those few outputs only have to agree to one spacing
     twice = _spmm(lib, comp, offs, (B * 2).contiguous(), M, N, K, split_k).cpu().numpy()
-    assert np.array_equal(twice, got * np.float16(2))
+    normal = np.abs(got) >= np.float16(2.0 ** -13)
+    assert np.array_equal(twice[normal], (got * np.float16(2))[normal])
+    assert np.all(np.abs(twice[~normal].astype(np.float32) - 2 * got[~normal].astype(np.float32)) <= 2.0 ** -23)
