@@ -17,6 +17,7 @@ from .api import (  # noqa: F401
     get_plan,
     launch_count,
     library,
+    set_launch_overlap,
     set_plan,
     splitk_reduction,
     spmm_splitk_no_alloc,

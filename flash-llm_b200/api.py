@@ -62,6 +62,7 @@ def library() -> C.CDLL:
     L.FlashLLM_SpMM_SplitK_NoAlloc.argtypes = [C.c_void_p] * 5 + [C.c_int] * 4
     L.FlashLLM_SplitK_Reduction.restype = C.c_int
     L.FlashLLM_SplitK_Reduction.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    L.FlashLLM_SetLaunchOverlap.argtypes = [C.c_int]
     L.FlashLLM_SetPlan.argtypes = [_i32p, C.c_int]
     L.FlashLLM_GetPlan.restype = C.c_int
     L.FlashLLM_GetPlan.argtypes = [C.c_int] * 4 + [_i32p, C.c_int]
@@ -161,6 +162,12 @@ def encode_on_device(stream: int, A_d: int, M: int, K: int, alloc_i32, alloc_u32
     comp_owner, comp_ptr = alloc_u32(max(words, 4))
     _check(library().FlashLLM_EncodeOnDevice_Pack(stream, A_d, M, K, offs_ptr, comp_ptr, 1), "EncodeOnDevice_Pack")
     return comp_owner, offs_owner, T + 2, words
+
+
+def set_launch_overlap(enable: bool) -> None:
+    """Let consecutive SpMM kernels of a stream overlap (set-up and weight streaming of the next start while the
+    previous drains).  Only valid when the compressed weights are not produced by work still running in that stream."""
+    library().FlashLLM_SetLaunchOverlap(1 if enable else 0)
 
 
 PLAN_FIELDS = ("cluster_k", "workspace_k", "a_stages", "b_stages", "b_batch", "ring_slots", "chunk_vectors",

@@ -253,6 +253,22 @@ __device__ __forceinline__ uint32_t umma_idesc_f16_f32(uint32_t m, uint32_t n)
     return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+
+// Lets the next kernel of the stream (if it was launched with the programmatic-serialisation attribute) start its
+// CTAs as soon as every CTA of this grid has executed this or exited.
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Blocks until every kernel this one depends on has completed and its writes are visible; returns at once for a
+// kernel that was launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- cluster
 
 __device__ __forceinline__ uint32_t cluster_ctarank()

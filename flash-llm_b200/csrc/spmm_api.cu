@@ -129,6 +129,7 @@ struct PlanOverride {
 };
 static PlanOverride g_override;
 static std::mutex   g_override_mutex;
+static std::atomic<int> g_launch_overlap{0};
 
 static int n_tile_for(int N)
 {
@@ -245,7 +246,7 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
 {
     const SpmmPlan&     pl = params.plan;
     cudaLaunchConfig_t  cfg{};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
     cfg.blockDim         = dim3((pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
@@ -256,6 +257,11 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     attr[0].val.clusterDim.z = 1;
     cfg.attrs                = attr;
     cfg.numAttrs             = 1;
+    if (g_launch_overlap.load(std::memory_order_relaxed)) {
+        attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs                                       = 2;
+    }
     count_launch();
     return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
 }
@@ -266,8 +272,18 @@ static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws
     const long long groups  = (count + 3) / 4;
     const unsigned  blocks  = static_cast<unsigned>((groups + threads - 1) / threads);
     count_launch();
-    splitk_reduce_f32_kernel<<<blocks, threads, 0, stream>>>(C, ws, count, parts);
-    return cudaGetLastError();
+    cudaLaunchConfig_t  cfg{};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim  = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.stream   = stream;
+    if (g_launch_overlap.load(std::memory_order_relaxed)) {
+        attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs                                          = attr;
+        cfg.numAttrs                                       = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_f32_kernel, C, ws, count, parts);
 }
 
 static cudaError_t reduce_workspace(cudaStream_t stream, half* C, const half* ws, long long count, int parts)
@@ -434,6 +450,11 @@ int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Works
         return static_cast<int>(cudaErrorInvalidValue);
     return static_cast<int>(reduce_workspace(static_cast<cudaStream_t>(stream), static_cast<half*>(C),
                                              static_cast<const half*>(Reduction_Workspace), count, Split_K));
+}
+
+void FlashLLM_SetLaunchOverlap(int enable)
+{
+    g_launch_overlap.store(enable ? 1 : 0, std::memory_order_relaxed);
 }
 
 void FlashLLM_SetPlan(const int* fields, int count)

@@ -328,6 +328,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_acc = *tmem_slot;
+    // A following kernel of this library may start its own set-up and weight streaming while this grid drains; it
+    // waits (below, in its B loader) before it touches anything this grid or its predecessors produce.
+    if (threadIdx.x == 0)
+        ptx::grid_launch_dependents();
 
     if (warp < P) {
         // ================================================================ producers: compressed stream
@@ -374,6 +378,10 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     else if (warp == b_warp) {
         // ================================================================ B loader: KB K tiles per TMA instruction
         if (lane == 0 && L > 0 && !(FLASHLLM_ABLATE & 32)) {
+            // B (and, through the MMAs that consume it, every store of this kernel) must come after the kernels
+            // before us in the stream; the compressed weights and their offsets are streamed without waiting, which
+            // is what the caller promises to be safe when it enables launch overlap.
+            ptx::grid_dependency_wait();
             const int batches = (L + KB - 1) / KB;
             int       bs      = 0;
             uint32_t  use     = 0;
@@ -733,6 +741,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 // C[i] = fp16(sum_s ws[s*count + i]); four outputs per thread.
 __global__ void splitk_reduce_f32_kernel(half* __restrict__ C, const float* __restrict__ ws, long long count, int parts)
 {
+    ptx::grid_launch_dependents();  // the next SpMM may begin streaming its weights
+    ptx::grid_dependency_wait();    // the partial matrices come from the SpMM launched just before
     const long long i4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
     if (i4 >= count)
         return;

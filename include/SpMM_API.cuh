@@ -135,6 +135,14 @@ int FlashLLM_SpMM_SplitK_NoAlloc(void*       stream,
  * C[i] = fp16(sum_s float(Workspace[s*M*N + i])). */
 int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K);
 
+/* Launch overlap (no counterpart in the reference).  With enable != 0, SpMM kernels are launched with programmatic
+ * stream serialisation: a kernel's CTAs may start while the previous kernel of the stream is still draining.  They
+ * set up, and stream Compressed_A / TileOffsets, right away; B is read and C / the workspace written only after
+ * everything enqueued before has completed.  The caller thereby promises that Compressed_A and TileOffsets of a call
+ * are not being produced by work still running in the same stream (weights resident before the calls, the inference
+ * case).  Off by default.  Process-wide. */
+void FlashLLM_SetLaunchOverlap(int enable);
+
 /* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
  * csrc/SpMM_API.cu:79-118): fixes launch-plan fields for subsequent calls from this process.  `fields` holds up to
  * nine ints, 0 = choose automatically, in this order:

@@ -186,3 +186,41 @@ def test_repeated_calls_and_streams(lib, oracle):
         with torch.cuda.stream(side if i % 2 else torch.cuda.current_stream()):
             got = prob.run()
         assert_close(got, want, f"call {i}")
+
+
+def test_launch_overlap_keeps_stream_order(lib, oracle):
+    """With launch overlap on, a kernel may start before its predecessor has finished, but must not read B or write C
+    early: a two-layer chain (the second SpMM's B is the first one's C), enqueued many times back to back."""
+    N, K1, M1, M2 = 16, 1024, 2048, 1024
+    A1 = lib.synthetic.sparse_uniform_matrix(M1, K1, 0.8, 61).numpy()
+    A2 = (lib.synthetic.sparse_uniform_matrix(M2, M1, 0.8, 62) * 0.05).to(torch.float16).numpy()
+    B_versions = [lib.synthetic.dense_uniform_matrix(N, K1, 70 + i).numpy() for i in range(4)]
+    c1, o1, _ = lib.InitSparseMatrixA_API(A1)
+    c2, o2, _ = lib.InitSparseMatrixA_API(A2)
+    dev = torch.device("cuda:0")
+    to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
+    c1_d, o1_d, c2_d, o2_d = to_dev(c1.view(np.int32)), to_dev(o1), to_dev(c2.view(np.int32)), to_dev(o2)
+    Bs = [to_dev(b) for b in B_versions]
+    X = torch.empty((N, K1), dtype=torch.float16, device=dev)
+    H = torch.empty((N, M1), dtype=torch.float16, device=dev)
+    ws = torch.empty((8, N, M1), dtype=torch.float16, device=dev)
+    outs = [torch.empty((N, M2), dtype=torch.float16, device=dev) for _ in range(12)]
+    stream = torch.cuda.current_stream().cuda_stream
+    want = []
+    for b in B_versions:
+        h = oracle.gemm_f32(A1, b).astype(np.float16)
+        want.append(oracle.gemm_f32(A2, h))
+    lib.set_launch_overlap(True)
+    try:
+        for i, out in enumerate(outs):
+            X.copy_(Bs[i % 4], non_blocking=True)
+            lib.SpMM_SplitK_API(stream, None, c1_d.data_ptr(), o1_d.data_ptr(), X.data_ptr(), H.data_ptr(), M1, N, K1,
+                                ws.data_ptr(), 8)
+            lib.SpMM_SplitK_API(stream, None, c2_d.data_ptr(), o2_d.data_ptr(), H.data_ptr(), out.data_ptr(), M2, N, M1,
+                                ws.data_ptr(), 8)
+        torch.cuda.synchronize()
+    finally:
+        lib.set_launch_overlap(False)
+    assert lib.consume_status() == 0
+    for i, out in enumerate(outs):
+        assert_close(out.cpu().numpy(), want[i % 4], f"chained call {i}")
