@@ -299,7 +299,7 @@ def run_ours(args) -> None:
                                  "plan": fl.get_plan(it["M"], N_TOKENS, it["K"], it["split_k"])}
     peak, peak_kind = measured_peak_gbs()
     dom = per_shape["ffn1"]
-    roofline = {"bound": "hbm", "kernel": "spmm_tcgen05_kernel<16> on the FFN1 shard", "achieved": dom["gbs"],
+    roofline = {"bound": "hbm", "kernel": "spmm_tcgen05_direct_kernel<16,16,4,2> on the FFN1 shard", "achieved": dom["gbs"],
                 "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": dom["gbs"] / peak,
                 "frac_of_nominal_8000": dom["gbs"] / 8000.0,
                 "traffic": DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * dom["bytes_alg"], "launch_ms": dom["ms"],

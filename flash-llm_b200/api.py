@@ -171,7 +171,8 @@ def set_launch_overlap(enable: bool) -> None:
 
 
 PLAN_FIELDS = ("cluster_k", "workspace_k", "a_stages", "b_stages", "b_batch", "ring_slots", "chunk_vectors",
-               "scatter_warps", "producers")
+               "scatter_warps", "producers", "path")
+PATH_RING, PATH_DIRECT = 1, 2
 
 
 def set_plan(**fields: int) -> None:

@@ -112,6 +112,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Asks the memory system to bring [src, src + bytes) into L2 (16-byte aligned address, size a multiple of 16); no
+// completion is signalled and nothing is written to shared memory or registers.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");

@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "../../include/SpMM_API.cuh"
+#include "spmm_kernel_direct_sm100.cuh"
 #include "spmm_kernel_sm100.cuh"
 #include "tiled_csl_host.h"
 #include "tiling.h"
@@ -53,16 +54,35 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 static EncodeTiledFn  g_encode_tiled = nullptr;
 static std::once_flag g_encode_once;
 
-template<int N_TILE>
-static cudaError_t raise_smem_limit(int optin)
+// Register budget of the register-streaming kernel: vectors per lane kept in registers (tiles of up to 768 vectors,
+// i.e. 62.5 % sparsity, need no overflow loop), for its two shapes: 8 scatter warps and one CTA per SM; 4 scatter
+// warps and two CTAs per SM.
+#ifndef FLASHLLM_NARROW_CAP
+#define FLASHLLM_NARROW_CAP 16
+#endif
+constexpr int kDirectCapWide = 24, kDirectCapNarrow = FLASHLLM_NARROW_CAP;
+
+template<typename Kernel>
+static cudaError_t raise_smem_limit_of(Kernel kernel, int optin)
 {
     cudaFuncAttributes attr{};
-    cudaError_t        e = cudaFuncGetAttributes(&attr, spmm_tcgen05_kernel<N_TILE>);
+    cudaError_t        e = cudaFuncGetAttributes(&attr, kernel);
     if (e != cudaSuccess)
         return e;
     // the opt-in limit covers static and dynamic shared memory together
-    return cudaFuncSetAttribute(spmm_tcgen05_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 optin - static_cast<int>(attr.sharedSizeBytes));
+}
+
+template<int N_TILE>
+static cudaError_t raise_smem_limit(int optin)
+{
+    cudaError_t e = raise_smem_limit_of(spmm_tcgen05_kernel<N_TILE>, optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapWide, 8, 1>, optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, 2>, optin);
+    return e;
 }
 
 static DeviceState* device_state(cudaError_t* err)
@@ -131,6 +151,8 @@ static PlanOverride g_override;
 static std::mutex   g_override_mutex;
 static std::atomic<int> g_launch_overlap{0};
 
+constexpr int kDefaultPath = kPathDirect;
+
 static int n_tile_for(int N)
 {
     return N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : 128));
@@ -168,8 +190,11 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
 
     // Two pipelines per SM (4 scatter warps, 4 stages each) where they fit; wide-N tiles need the shared memory for
     // their B batches, so they run one deeper pipeline per SM instead.
-    const bool two_per_sm = pl.n_tile <= 32;
-    pl.scatter_warps   = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps] : (two_per_sm ? 4 : 8);
+    pl.path               = ov.v[kPlanPath] ? ov.v[kPlanPath] : kDefaultPath;
+    const bool direct     = pl.path == kPathDirect;
+    pl.scatter_warps      = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps]
+                                                    : (direct ? (pl.n_tile <= 64 ? 4 : 8) : (pl.n_tile <= 32 ? 4 : 8));
+    const bool two_per_sm = direct ? pl.scatter_warps == 4 : pl.n_tile <= 32;
     pl.producers       = ov.v[kPlanProducers] ? ov.v[kPlanProducers] : 1;
     pl.chunk_vectors   = ov.v[kPlanChunkVectors] ? ov.v[kPlanChunkVectors] : 512;
     pl.ring_slots      = ov.v[kPlanRingSlots] ? ov.v[kPlanRingSlots]
@@ -179,26 +204,41 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     pl.a_stages        = ov.v[kPlanAStages] ? ov.v[kPlanAStages] : pl.scatter_warps;
     pl.b_batch         = ov.v[kPlanBBatch] ? ov.v[kPlanBBatch] : (4096 / slab > 0 ? 4096 / slab : 1);
     pl.b_stages        = ov.v[kPlanBStages] ? ov.v[kPlanBStages] : 2;
+    if (direct) {  // one stage per scatter warp, no copy ring; B batches split evenly between the MMA issuers
+        if (!ov.v[kPlanBBatch])
+            pl.b_batch = (pl.b_batch + kDirectIssuers - 1) / kDirectIssuers * kDirectIssuers;
+        pl.a_stages      = pl.scatter_warps;
+        pl.producers     = 0;
+        pl.ring_slots    = 0;
+        pl.chunk_vectors = 0;
+    }
 
-    // How to cut K.  A CTA that owns a whole tile row needs no reduction and pays its pipeline fill once, so K is
-    // split only when the tile rows alone leave most CTA slots empty.  Parts that go through the caller's workspace
-    // (fp32 partial matrices, summed by a second kernel; at most Split_K/2 of them) measured cheaper than parts of a
-    // thread-block cluster (summed through distributed shared memory), whose CTAs must be co-scheduled; clusters
-    // take what the workspace cannot.  Replaces the reference's hand-tuned Split_K tables
+    // How to cut K.  A CTA that owns a whole tile row needs no reduction and pays its pipeline fill once, so K is cut
+    // only to fill the GPU: with `slots` CTAs resident at a time, G parts per tile row run in ceil(rows*G/slots)
+    // waves, and the best G is the one whose last wave is fullest (measured on 216 tile rows and 296 slots: 2, 3 parts
+    // gain nothing, 4 parts +8 %).  Parts that go through the caller's workspace (fp32 partial matrices summed by a
+    // second kernel; at most Split_K/2 of them) are cheaper than parts of a thread-block cluster (summed through
+    // distributed shared memory, CTAs co-scheduled) except on small problems, where the second launch costs more than
+    // it saves; clusters also take what the workspace cannot.  Replaces the reference's hand-tuned Split_K tables
     // (kernel_benchmark/benchmark.sh:13-15).
     const int slots     = st->sm_count * (two_per_sm ? 2 : 1);
     const int max_extra = ((static_cast<long long>(M) * N) % 4 != 0) ? 1 : (Split_K / 2 > 1 ? Split_K / 2 : 1);
-    int       best_s = 1, best_g = 1;
-    if (ctas_flat * 10 < slots * 6) {
-        int want = (slots + ctas_flat / 2) / ctas_flat;
-        if (want < 1)
-            want = 1;
-        if (want > k_tiles)
-            want = k_tiles;
-        best_g = want < max_extra ? want : max_extra;
-        if (best_g > 8)
-            best_g = 8;
-        best_s = (want + best_g / 2) / best_g;
+    const bool small    = static_cast<long long>(tile_rows) * k_tiles <= 4096;
+    int        best_s = 1, best_g = 1;
+    if (!small) {
+        double best_score = -1.0;
+        for (int g = 1; g <= max_extra && g <= 8 && g <= k_tiles; ++g) {
+            const double x     = static_cast<double>(ctas_flat) * g / slots;
+            const double waves = static_cast<double>(static_cast<long long>(x + 0.999999));
+            const double score = x / waves - 0.015 * (g - 1);
+            if (score > best_score) {
+                best_score = score;
+                best_g     = g;
+            }
+        }
+    }
+    if (static_cast<long long>(ctas_flat) * best_g * 10 < static_cast<long long>(slots) * 6) {
+        best_s = slots / (ctas_flat * best_g);
         if (best_s < 1)
             best_s = 1;
         if (best_s > kMaxClusterK)
@@ -222,13 +262,17 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
     pl.smem_bytes     = plan_smem_bytes(pl);
 
-    const bool ok = pl.scatter_warps >= 4 && pl.scatter_warps <= kMaxScatterWarps
-                    && pl.producers >= 1 && pl.producers <= kMaxProducers && is_pow2(pl.chunk_vectors)
-                    && pl.chunk_vectors >= 64 && pl.ring_slots <= kMaxRingSlots
-                    // a slot is always refilled by the same producer warp, and a stage's successive tiles are taken by
-                    // groups that cannot be two uses ahead: both keep every mbarrier parity wait within one phase
-                    && pl.ring_slots % pl.producers == 0 && pl.a_stages >= pl.scatter_warps
-                    && pl.ring_slots * pl.chunk_vectors >= kMaxTileVectors + pl.chunk_vectors
+    const bool ring_ok = pl.scatter_warps >= 4 && pl.scatter_warps <= kMaxScatterWarps
+                         && pl.producers >= 1 && pl.producers <= kMaxProducers && is_pow2(pl.chunk_vectors)
+                         && pl.chunk_vectors >= 64 && pl.ring_slots <= kMaxRingSlots
+                         // a slot is always refilled by the same producer warp, and a stage's successive tiles are
+                         // taken by groups that cannot be two uses ahead: both keep every mbarrier parity wait within
+                         // one phase
+                         && pl.ring_slots % pl.producers == 0 && pl.a_stages >= pl.scatter_warps
+                         && pl.ring_slots * pl.chunk_vectors >= kMaxTileVectors + pl.chunk_vectors;
+    const bool direct_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8)
+                           && pl.a_stages == pl.scatter_warps && pl.b_batch % kDirectIssuers == 0;
+    const bool ok = (pl.path == kPathRing || pl.path == kPathDirect) && (direct ? direct_ok : ring_ok)
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
                     && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
@@ -248,7 +292,8 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cudaLaunchConfig_t  cfg{};
     cudaLaunchAttribute attr[2];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
-    cfg.blockDim         = dim3((pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
+    cfg.blockDim         = dim3((pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps
+                                                            : pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream           = stream;
     attr[0].id               = cudaLaunchAttributeClusterDimension;
@@ -263,6 +308,11 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
         cfg.numAttrs                                       = 2;
     }
     count_launch();
+    if (pl.path == kPathDirect) {
+        if (pl.scatter_warps == 8)
+            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapWide, 8, 1>, tmap, params);
+        return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, 2>, tmap, params);
+    }
     return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
 }
 
@@ -475,8 +525,9 @@ int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count)
     SpmmPlan pl{};
     if ((err = make_plan(st, M, N, K, Split_K, &pl)) != cudaSuccess)
         return static_cast<int>(err);
-    const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k, pl.a_stages,      pl.b_stages,   pl.b_batch,
-                                             pl.ring_slots, pl.chunk_vectors, pl.scatter_warps, pl.producers,  pl.smem_bytes};
+    const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k,   pl.a_stages,      pl.b_stages,  pl.b_batch,
+                                             pl.ring_slots, pl.chunk_vectors, pl.scatter_warps, pl.producers, pl.path,
+                                             pl.smem_bytes};
     for (int i = 0; i < count && i <= kPlanFieldCount; ++i)
         out[i] = values[i];
     return 0;

@@ -1,0 +1,502 @@
+// Load-as-Sparse / Compute-as-Dense SpMM for sm_100a, register-streaming form.
+//
+// Same work, roles of the B loader, MMA issuer and epilogue, K split and bounded waits as spmm_tcgen05_kernel, but
+// the compressed words never pass through shared memory as a stream:
+//
+//   * Every scatter warp owns one 16 KB stage and takes every NSW-th tile of the CTA's K range.  It fetches the words
+//     of its NEXT tile straight from global memory into registers (ld.global.nc, 16 bytes per lane and instruction,
+//     the reference's LDG.128 scheme, csrc/SpMM_Kernel.cuh:17-62) right after it has published the current one, so
+//     a whole hand-back period of the stage (several microseconds) hides the memory latency, and as many tiles as
+//     there are scatter warps are in flight per CTA.  No copy ring, no producer warps, no per-chunk barriers.
+//   * The scatter warps are bound by latency chains and by the instructions they issue per tile, not by
+//     shared-memory bandwidth, so a stage is cleared with 32 16-byte stores per lane, which take fewer instructions
+//     than any per-word scheme.  Tiles with more vectors than the register budget (CAP per lane) fetch and scatter
+//     the excess in a plain loop.
+#pragma once
+#include "spmm_kernel_sm100.cuh"
+
+namespace flashllm {
+
+__device__ __forceinline__ uint4 ldg_stream16(const uint4* ptr)
+{
+    uint4 v;
+#ifndef FLASHLLM_LDG_FLAVOUR
+#define FLASHLLM_LDG_FLAVOUR "ld.global.nc.L1::no_allocate.v4.u32"
+#endif
+    asm volatile(FLASHLLM_LDG_FLAVOUR " {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(ptr));
+    return v;
+}
+
+// smem[stage + 2*loc] = value for one tiled-CSL word; locations are masked to the 8192 cells of a tile, so a corrupt
+// word cannot leave the stage.
+__device__ __forceinline__ void scatter_word_aligned(uint32_t stage, uint32_t word)
+{
+#if (FLASHLLM_ABLATE & 64)
+    // timing only: a full-word store of the same instruction count (wrong values)
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage + ((word >> 15) & 0x3FFCu)), "r"(word) : "memory");
+#else
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + ((word >> 15) & 0x3FFEu)),
+                 "h"(static_cast<unsigned short>(word & 0xFFFFu))
+                 : "memory");
+#endif
+}
+
+__device__ __forceinline__ void scatter_vector_aligned(uint32_t stage, const uint4& w)
+{
+    scatter_word_aligned(stage, w.x);
+    scatter_word_aligned(stage, w.y);
+    scatter_word_aligned(stage, w.z);
+    scatter_word_aligned(stage, w.w);
+}
+
+// Warps of the register-streaming kernel: one B loader, kDirectIssuers MMA issuers, then the scatter warps.
+constexpr int kDirectIssuers = 2;
+
+// CAP: vectors per lane kept in registers (a tile of up to 32*CAP vectors is handled without the overflow loop).
+// WARPS: scatter warps = stages.  MIN_BLOCKS: CTAs per SM the register budget is sized for.
+//
+// One thread cannot issue tcgen05.mma as fast as the tensor core retires them (measured: 4 MMAs and the commit that
+// hands a stage back cost an issuing thread ~400 cycles, the tensor core ~180), so tiles alternate between
+// kDirectIssuers issuing threads, each with an accumulator of its own in tensor memory; the epilogue adds them.
+template<int N_TILE, int CAP, int WARPS, int MIN_BLOCKS>
+__global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
+    spmm_tcgen05_direct_kernel(const __grid_constant__ CUtensorMap tmap_b, const SpmmParams p)
+{
+    static_assert(N_TILE == 16 || N_TILE == 32 || N_TILE == 64 || N_TILE == 128, "unsupported MMA N");
+    static_assert(WARPS >= 4 && WARPS <= 12, "four warps cover the TMEM lane quarters in the epilogue");
+    constexpr uint32_t kBSlab    = N_TILE * kTileK * 2;  // one K tile of B in shared memory
+    constexpr int      MI        = kDirectIssuers;
+    static_assert(WARPS % MI == 0, "every issuer serves the same stages on every lap");
+    constexpr uint32_t kTmemCols = MI * N_TILE < 32 ? 32 : MI * N_TILE;  // a power of two for MI = 2
+    constexpr int      NSW       = WARPS;
+    constexpr int      a_stages  = WARPS;
+
+#ifdef FLASHLLM_TRACE
+    __shared__ unsigned int s_trace[kTraceKinds * kTraceDepth];
+    for (int i = threadIdx.x; i < kTraceKinds * kTraceDepth; i += blockDim.x)
+        s_trace[i] = 0;
+#endif
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base     = (raw_addr + 1023u) & ~1023u;  // swizzled operands need 1024-byte alignment
+    uint8_t* const smem     = smem_raw + (base - raw_addr);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const SpmmPlan& plan     = p.plan;
+    const int       b_stages = plan.b_stages;
+    const int       KB       = plan.b_batch;
+    const int       S        = plan.cluster_k;
+    const int       G        = plan.workspace_k;
+    constexpr int   b_warp   = 0;  // warp that loads B
+    constexpr int   mma_warp = 1;       // first of the MI warps that issue MMAs; it owns the TMEM allocation
+    constexpr int   first_sw = 1 + MI;  // first scatter warp
+    constexpr int   NTS      = NSW * 32;
+
+    // ---- shared memory carve-up
+    const uint32_t a_base   = base;
+    const uint32_t b_base   = a_base + a_stages * kDenseTileBytes;
+    const uint32_t bar_base = b_base + b_stages * KB * kBSlab;
+    const uint32_t a_full   = bar_base;
+    const uint32_t a_empty  = a_full + 8u * a_stages;
+    const uint32_t b_full   = a_empty + 8u * a_stages;
+    const uint32_t b_empty  = b_full + 8u * b_stages;
+    const uint32_t acc_full = b_empty + 8u * b_stages;
+    const uint32_t misc_off = (acc_full + 8u) - base;
+    volatile uint32_t* const tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem + misc_off);
+    volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(smem + misc_off + 4);
+    int* const               offs_stage = reinterpret_cast<int*>(smem + misc_off + 16);  // plan.offsets_staged ints
+
+    // ---- work assignment: blockIdx.x = K part inside the cluster, y = tile row, z = (N tile, workspace part)
+    const int rank     = blockIdx.x;
+    const int tile_row = blockIdx.y;
+    const int g        = blockIdx.z % G;
+    const int n_idx    = blockIdx.z / G;
+    const int parts    = S * G;
+    const int part     = g * S + rank;
+    const int k_begin  = static_cast<int>(static_cast<long long>(p.k_tiles) * part / parts);
+    const int k_end    = static_cast<int>(static_cast<long long>(p.k_tiles) * (part + 1) / parts);
+    const int L        = k_end - k_begin;
+    const int* const offs_global = p.tile_offsets + static_cast<long long>(tile_row) * p.k_tiles + k_begin;
+    const bool       staged      = (L + 1 <= plan.offsets_staged);
+    const int* const offs        = staged ? offs_stage : offs_global;  // valid after the set-up barrier
+
+    if (raw_addr != base) {  // the launch did not honour the 1024-byte alignment: nothing below would be valid
+        if (threadIdx.x == 0)
+            atomicOr(p.status, kStatusSmemMisaligned);
+        return;
+    }
+
+    // ---- set-up
+    if (threadIdx.x == 0) {
+        // An earlier CTA that gave up leaves the status word set; later CTAs then skip their work.
+        const unsigned int status_now = *reinterpret_cast<volatile unsigned int*>(p.status);
+        for (int i = 0; i < a_stages; ++i) {
+            ptx::mbar_init(a_full + 8u * i, 1);
+            ptx::mbar_init(a_empty + 8u * i, 1);
+        }
+        for (int i = 0; i < b_stages; ++i) {
+            ptx::mbar_init(b_full + 8u * i, 1);
+            ptx::mbar_init(b_empty + 8u * i, MI);  // every issuer hands a batch back
+        }
+        ptx::mbar_init(acc_full, MI);
+        *abort_flag = (status_now != 0u) ? 1u : 0u;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == mma_warp) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    if (staged) {
+        // This CTA's slice of TileOffsets is read once, together, instead of one dependent load per tile.
+        for (int i = threadIdx.x; i <= L; i += blockDim.x)
+            offs_stage[i] = offs_global[i];
+    }
+    // Offsets that run backwards, or tiles above 2048 vectors, would make the roles below disagree about who owns
+    // which vectors; the whole slice is checked before any of them starts.
+    bool bad_slice = false;
+    for (int i = threadIdx.x; i < L; i += blockDim.x) {
+        const int lo = offs_global[i], hi = offs_global[i + 1];
+        bad_slice |= (lo < 0) || (hi < lo) || (hi - lo > kMaxTileVectors);
+    }
+    ptx::tc_fence_before_sync();
+    bad_slice = __syncthreads_or(bad_slice ? 1 : 0) != 0;
+    ptx::tc_fence_after_sync();
+    const bool go = !bad_slice && (*abort_flag == 0u);  // false: every role skips its work and nothing is stored
+    if (bad_slice && threadIdx.x == 0) {
+        atomicOr(p.status, kStatusBadTileOffsets);
+        *abort_flag = 1u;
+    }
+    const uint32_t tmem_acc = *tmem_slot;
+    // A following kernel of this library may start its set-up and weight streaming while this grid drains; it waits
+    // (in its B loader) before it touches anything this grid or its predecessors produce.
+    if (threadIdx.x == 0)
+        ptx::grid_launch_dependents();
+
+    if (warp == b_warp) {
+        // ================================================================ B loader: KB K tiles per TMA instruction
+        if (lane == 0 && L > 0 && go) {
+            ptx::grid_dependency_wait();
+            const int batches = (L + KB - 1) / KB;
+            int       bs      = 0;
+            uint32_t  use     = 0;
+            int       issued  = 0;
+            for (int b = 0; b < batches; ++b) {
+                if (!wait_bounded_relaxed(b_empty + 8u * bs, (use & 1u) ^ 1u, abort_flag, p.status))
+                    break;
+                const uint32_t bar = b_full + 8u * bs;
+                ptx::mbar_arrive_expect_tx(bar, KB * kBSlab);
+                ptx::tma_load_3d(b_base + bs * KB * kBSlab, &tmap_b, 0, n_idx * N_TILE, k_begin + b * KB, bar);
+                ++issued;
+                if (++bs == b_stages) {
+                    bs = 0;
+                    ++use;
+                }
+            }
+            if (*abort_flag) {
+                // Give copies already issued a bounded chance to land before the CTA may exit.
+                const uint64_t t_leave = ptx::globaltimer_ns();
+                for (int back = 1; back <= b_stages && back <= issued; ++back) {
+                    const int      bb  = issued - back;
+                    const uint32_t bar = b_full + 8u * (bb % b_stages);
+                    while (!ptx::mbar_test_wait(bar, (bb / b_stages) & 1u)
+                           && ptx::globaltimer_ns() - t_leave < 2000000ull) {}
+                }
+            }
+        }
+    }
+    else if (warp < first_sw) {
+        // ================================================================ MMA issuers: issuer m takes tiles m, m + MI, ...
+        // The B batches hold a multiple of MI tiles, so every issuer has work in every full batch and hands it back
+        // itself; the last, partial batch is never waited for.
+        if (lane == 0 && go) {
+            const int m = warp - mma_warp;
+            if (m < L) {
+                const uint32_t idesc   = ptx::umma_idesc_f16_f32(kTileM, N_TILE);
+                const uint64_t a_desc0 = ptx::umma_desc_kmajor_sw128(a_base);
+                const uint64_t b_desc0 = ptx::umma_desc_kmajor_sw128(b_base);
+                const uint32_t acc     = tmem_acc + static_cast<uint32_t>(m * N_TILE);
+                int            s = m, bs = 0, kb = m;
+                uint32_t       a_par = 0, b_par = 0;
+                bool           ready = false, first_in_batch = true;
+                for (int j = m; j < L; j += MI) {
+                    if (m == 0)
+                        FL_TRACE(7, j);
+                    if (!ready) {
+                        if (!wait_bounded(a_full + 8u * s, a_par, abort_flag, p.status))
+                            break;
+                        if (first_in_batch && !wait_bounded(b_full + 8u * bs, b_par, abort_flag, p.status))
+                            break;
+                    }
+                    if (m == 0)
+                        FL_TRACE(9, j);
+                    int      s_n = s + MI, kb_n = kb + MI, bs_n = bs;
+                    uint32_t a_par_n = a_par, b_par_n = b_par;
+                    if (s_n >= a_stages) {
+                        s_n -= a_stages;
+                        a_par_n ^= 1u;
+                    }
+                    const bool batch_done = kb_n >= KB;
+                    if (batch_done) {
+                        kb_n -= KB;
+                        if (++bs_n == b_stages) {
+                            bs_n = 0;
+                            b_par_n ^= 1u;
+                        }
+                    }
+                    const bool has_next = j + MI < L;
+                    ptx::tc_fence_after_sync();
+#if (FLASHLLM_ABLATE & 4)
+                    ptx::umma_commit(a_empty + 8u * s);  // timing only: hand-backs without any MMA
+                    if (batch_done || !has_next)
+                        ptx::umma_commit(b_empty + 8u * bs);
+                    ready = false;
+                    if (false)
+#endif
+                    ready = ptx::umma_tile_commit_probe(
+                        acc, a_desc0 + static_cast<uint32_t>(s * (kDenseTileBytes >> 4)),
+                        b_desc0 + static_cast<uint32_t>((bs * KB + kb) * (kBSlab >> 4)), idesc, j != m ? 1u : 0u, a_empty + 8u * s,
+                        b_empty + 8u * bs, (batch_done || !has_next) ? 1u : 0u, a_full + 8u * s_n, a_par_n, b_full + 8u * bs_n,
+                        b_par_n, has_next ? 1u : 0u, (has_next && batch_done) ? 1u : 0u);
+                    if (m == 0)
+                        FL_TRACE(10, j);
+                    first_in_batch = batch_done;
+                    s     = s_n;
+                    kb    = kb_n;
+                    bs    = bs_n;
+                    a_par = a_par_n;
+                    b_par = b_par_n;
+                }
+            }
+            ptx::umma_commit(acc_full);
+        }
+    }
+    else {
+        // ================================================================ scatter warps: one stage each
+        const int sw = warp - first_sw;
+        if (L > 0 && go) {
+            const uint32_t stage     = a_base + sw * kDenseTileBytes;
+            const uint32_t full_bar  = a_full + 8u * sw;
+            const uint32_t empty_bar = a_empty + 8u * sw;
+            uint4          nxt[CAP];  // words of the tile about to be scattered (loads in flight)
+#pragma unroll
+            for (int q = 0; q < CAP; ++q)
+                nxt[q] = make_uint4(0u, 0u, 0u, 0u);
+
+            int          n_in = 0;  // vectors of the tile in nxt
+            const uint4* src  = p.compressed;
+            bool         bad  = false;
+            // ---- first tile of this warp
+            if (sw < L) {
+                const int vb = offs[sw], ve = offs[sw + 1];
+                bad          = (ve < vb) || (ve - vb > kMaxTileVectors) || (vb < 0);
+                n_in         = bad ? 0 : ve - vb;
+                src          = p.compressed + (bad ? 0 : vb);
+#pragma unroll
+                for (int q = 0; q < CAP; ++q) {
+                    if (q * 32 >= n_in)
+                        break;  // a real branch: blocks past the tile's end are skipped, not issued predicated off
+                    if (q * 32 + lane < n_in)
+                        nxt[q] = ldg_stream16(src + q * 32 + lane);
+                }
+                if (lane == 0 && sw + NSW < L && offs[sw + NSW + 1] > offs[sw + NSW])
+                    ptx::prefetch_l2_bulk(p.compressed + offs[sw + NSW],
+                                          static_cast<uint32_t>(offs[sw + NSW + 1] - offs[sw + NSW]) * 16u);
+            }
+            uint32_t use = 0;
+            for (int j = sw; j < L; j += NSW, ++use) {
+                // offsets of this warp's following tile, fetched a whole tile ahead of their use
+                const bool has_next = j + NSW < L;
+                int        vb2 = 0, ve2 = 0;
+                if (has_next) {
+                    vb2 = offs[j + NSW];
+                    ve2 = offs[j + NSW + 1];
+                }
+                if (bad)
+                    atomicOr(p.status, kStatusBadTileOffsets);
+                if (lane == 0)
+                    FL_TRACE(0, j);
+                bool ok = !bad;
+                if (ok && use > 0)
+                    ok = wait_bounded_warp(empty_bar, (use & 1u) ^ 1u, abort_flag, p.status);
+                if (!ok) {  // uniform across the warp
+                    if (bad)
+                        *abort_flag = 1u;
+                    break;
+                }
+                if (lane == 0)
+                    FL_TRACE(3, j);
+                // ---- clear the stage, then scatter the new tile
+                if (!(FLASHLLM_ABLATE & 1))
+                    zero_fill_stage(stage, lane);
+                __syncwarp();  // another lane's zero must not land on top of this lane's new value
+                if (lane == 0)
+                    FL_TRACE(2, j);
+                const int n_reg = n_in < CAP * 32 ? n_in : CAP * 32;
+#pragma unroll
+                for (int q = 0; q < CAP; ++q) {
+                    if (q * 32 >= n_reg)
+                        break;
+                    if (q * 32 + lane < n_reg) {
+#if (FLASHLLM_ABLATE & 2)
+                        if ((nxt[q].x ^ nxt[q].y ^ nxt[q].z ^ nxt[q].w) == 0x9E3779B9u)  // keeps the loads alive
+                            scatter_word_aligned(stage, nxt[q].x);
+#else
+                        scatter_vector_aligned(stage, nxt[q]);
+#endif
+                    }
+                }
+
+                // tiles denser than the register budget: the rest in further register loads, fetched only now
+                for (int v0 = n_reg; v0 < n_in; v0 += CAP * 32) {
+#pragma unroll
+                    for (int q = 0; q < CAP; ++q) {
+                        if (v0 + q * 32 >= n_in)
+                            break;
+                        if (v0 + q * 32 + lane < n_in)
+                            nxt[q] = ldg_stream16(src + v0 + q * 32 + lane);
+                    }
+#pragma unroll
+                    for (int q = 0; q < CAP; ++q) {
+                        if (v0 + q * 32 >= n_in)
+                            break;
+                        if (v0 + q * 32 + lane < n_in)
+                            scatter_vector_aligned(stage, nxt[q]);
+                    }
+                }
+                if (lane == 0)
+                    FL_TRACE(5, j);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(full_bar);
+                if (lane == 0)
+                    FL_TRACE(6, j);
+                // ---- start fetching the following tile
+                if (has_next) {
+                    bad  = (ve2 < vb2) || (ve2 - vb2 > kMaxTileVectors) || (vb2 < 0);
+                    n_in = bad ? 0 : ve2 - vb2;
+                    src  = p.compressed + (bad ? 0 : vb2);
+#pragma unroll
+                    for (int q = 0; q < CAP; ++q) {
+                        if (q * 32 >= n_in)
+                            break;
+                        if (q * 32 + lane < n_in && !(FLASHLLM_ABLATE & 8))
+                            nxt[q] = ldg_stream16(src + q * 32 + lane);
+                    }
+                    // ... and pull the one after it from DRAM into L2, so that its register loads, issued one tile
+                    // from now, only have the L2 latency left to hide
+                    if (lane == 0 && j + 2 * NSW < L) {
+                        const int pb = offs[j + 2 * NSW], pe = offs[j + 2 * NSW + 1];
+                        if (pe > pb)
+                            ptx::prefetch_l2_bulk(p.compressed + pb, static_cast<uint32_t>(pe - pb) * 16u);
+                    }
+                }
+                if (lane == 0)
+                    FL_TRACE(13, j);
+            }
+        }
+
+        // ================================================================ epilogue (same warps)
+        bool acc_ok = go;
+        if (L > 0 && go)
+            acc_ok = wait_bounded_warp(acc_full, 0u, abort_flag, p.status);
+        acc_ok = __all_sync(0xFFFFFFFFu, acc_ok && (*abort_flag == 0u));
+        ptx::tc_fence_after_sync();
+
+        const int quarter     = warp & 3;  // TMEM lanes this warp may read: 32*quarter ..
+        constexpr int per_quarter = NSW >= 8 ? 2 : 1;  // warps sharing a lane quarter split the columns
+        const int col_share   = (N_TILE / per_quarter) < 8 ? 8 : (N_TILE / per_quarter);
+        const int col_begin   = sw < 4 * per_quarter ? (sw / 4) * col_share : N_TILE;  // the remaining warps idle
+        const int col_end     = (col_begin + col_share) < N_TILE ? (col_begin + col_share) : N_TILE;
+        const int n_valid     = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
+        const int row_in_tile = quarter * 32 + lane;
+        const size_t tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
+        half* const  out_tile  = p.out + tile_off;
+        float* const part_tile = G > 1 ? p.partial + static_cast<size_t>(g) * p.M * p.N + tile_off : nullptr;
+        float* const red       = reinterpret_cast<float*>(smem);  // [N_TILE][128] fp32, over the idle A stages
+
+        for (int c0 = col_begin; c0 < col_end; c0 += 8) {
+            uint32_t r[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                r[i] = 0u;
+            for (int m = 0; m < MI && m < L; ++m) {  // an issuer without tiles never wrote its accumulator
+                uint32_t t[8];
+                ptx::tmem_ld_x8(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + m * N_TILE + c0, t);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(t[i]));
+            }
+            if (S == 1) {
+                if (acc_ok) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (c0 + i < n_valid) {
+                            const size_t at = static_cast<size_t>(c0 + i) * p.M + row_in_tile;
+                            if (part_tile)
+                                part_tile[at] = __uint_as_float(r[i]);
+                            else
+                                out_tile[at] = __float2half_rn(__uint_as_float(r[i]));
+                        }
+                }
+            }
+            else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    red[(c0 + i) * kTileM + row_in_tile] = __uint_as_float(r[i]);
+            }
+        }
+    }
+
+    // ================================================================ cluster reduction and tear-down
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (S > 1) {
+        __syncwarp();
+        ptx::cluster_sync_all();  // every CTA's partial tile is parked in its shared memory
+        if (warp >= first_sw) {
+            const int    tid_s    = threadIdx.x - first_sw * 32;
+            const int    n_valid  = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
+            const int    total    = N_TILE * kTileM;
+            const int    lo       = static_cast<int>(static_cast<long long>(total) * rank / S);
+            const int    hi       = static_cast<int>(static_cast<long long>(total) * (rank + 1) / S);
+            const bool   store_ok = (*abort_flag == 0u);
+            const size_t tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
+            half* const  out_tile  = p.out + tile_off;
+            float* const part_tile = G > 1 ? p.partial + static_cast<size_t>(g) * p.M * p.N + tile_off : nullptr;
+            for (int e = lo + tid_s; e < hi; e += NTS) {
+                const int n = e / kTileM, m = e % kTileM;
+                if (n >= n_valid)
+                    break;
+                float acc = 0.0f;
+                for (int q = 0; q < S; ++q)
+                    acc += ptx::ld_dsmem_f32(ptx::map_to_rank(base + static_cast<uint32_t>(e) * 4u, q));
+                if (store_ok) {
+                    if (part_tile)
+                        part_tile[static_cast<size_t>(n) * p.M + m] = acc;
+                    else
+                        out_tile[static_cast<size_t>(n) * p.M + m] = __float2half_rn(acc);
+                }
+            }
+        }
+        __syncwarp();
+        ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+    }
+    if (warp == mma_warp) {
+        __syncwarp();
+        ptx::tmem_dealloc(tmem_acc, kTmemCols);
+    }
+#ifdef FLASHLLM_TRACE
+    if (blockIdx.y == FLASHLLM_TRACE && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < kTraceKinds * kTraceDepth; i += blockDim.x)
+            g_trace[i] = s_trace[i];
+#endif
+}
+
+}  // namespace flashllm

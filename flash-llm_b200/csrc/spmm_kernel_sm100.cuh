@@ -324,9 +324,21 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         for (int i = threadIdx.x; i <= L; i += blockDim.x)
             offs_stage[i] = offs_global[i];
     }
+    // Offsets that run backwards, or tiles above 2048 vectors, would make the roles below disagree about who owns
+    // which vectors; the whole slice is checked before any of them starts.
+    bool bad_slice = false;
+    for (int i = threadIdx.x; i < L; i += blockDim.x) {
+        const int lo = offs_global[i], hi = offs_global[i + 1];
+        bad_slice |= (lo < 0) || (hi < lo) || (hi - lo > kMaxTileVectors);
+    }
     ptx::tc_fence_before_sync();
-    __syncthreads();
+    bad_slice = __syncthreads_or(bad_slice ? 1 : 0) != 0;
     ptx::tc_fence_after_sync();
+    const bool go = !bad_slice && (*abort_flag == 0u);  // false: every role skips its work and nothing is stored
+    if (bad_slice && threadIdx.x == 0) {
+        atomicOr(p.status, kStatusBadTileOffsets);
+        *abort_flag = 1u;
+    }
     const uint32_t tmem_acc = *tmem_slot;
     // A following kernel of this library may start its own set-up and weight streaming while this grid drains; it
     // waits (below, in its B loader) before it touches anything this grid or its predecessors produce.
@@ -335,7 +347,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 
     if (warp < P) {
         // ================================================================ producers: compressed stream
-        if (lane == 0 && L > 0) {
+        if (lane == 0 && L > 0 && go) {
             const int v_first = offs[0];
             int       nvec    = offs[L] - v_first;
             if (nvec < 0)
@@ -377,7 +389,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     }
     else if (warp == b_warp) {
         // ================================================================ B loader: KB K tiles per TMA instruction
-        if (lane == 0 && L > 0 && !(FLASHLLM_ABLATE & 32)) {
+        if (lane == 0 && L > 0 && go && !(FLASHLLM_ABLATE & 32)) {
             // B (and, through the MMAs that consume it, every store of this kernel) must come after the kernels
             // before us in the stream; the compressed weights and their offsets are streamed without waiting, which
             // is what the caller promises to be safe when it enables launch overlap.
@@ -413,7 +425,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         // ================================================================ MMA issuer (tile order)
         // Per tile: four MMAs, the commit that hands the stage back, and a probe of the next tile's barriers issued
         // ahead of the MMAs so that its round trip is hidden behind them.
-        if (lane == 0 && L > 0) {
+        if (lane == 0 && L > 0 && go) {
             const uint32_t idesc   = ptx::umma_idesc_f16_f32(kTileM, N_TILE);
             const uint64_t a_desc0 = ptx::umma_desc_kmajor_sw128(a_base);
             const uint64_t b_desc0 = ptx::umma_desc_kmajor_sw128(b_base);
@@ -464,7 +476,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
     else {
         // ================================================================ scatter warps: one whole tile at a time
         const int sw = warp - first_sw;  // scatter warp index
-        if (L > 0) {
+        if (L > 0 && go) {
             const int v_first = offs[0];
             // Stage and ring-slot indices advance by repeated subtraction: a runtime division costs the warp more than
             // a hundred cycles of dependent latency, several times per tile.
@@ -642,8 +654,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         }
 
         // ================================================================ epilogue (same warps)
-        bool acc_ok = true;
-        if (L > 0)
+        bool acc_ok = go;
+        if (L > 0 && go)
             acc_ok = wait_bounded_warp(acc_full, 0u, abort_flag, p.status);
         acc_ok = __all_sync(0xFFFFFFFFu, acc_ok && (*abort_flag == 0u));
         ptx::tc_fence_after_sync();

@@ -60,14 +60,15 @@ class DeviceProblem:
         self.C = torch.full((N, M), float("nan"), dtype=torch.float16, device=dev)
         self.ws = torch.empty((max(split_k, 1), N, M), dtype=torch.float16, device=dev)
 
-    def run(self) -> np.ndarray:
+    def run(self, check_status: bool = True) -> np.ndarray:
         self.C.fill_(float("nan"))
         stream = torch.cuda.current_stream().cuda_stream
         self.fl.SpMM_SplitK_API(stream, None, self.comp.data_ptr(), self.offs.data_ptr(), self.B.data_ptr(),
                                 self.C.data_ptr(), self.M, self.N, self.K, self.ws.data_ptr(), self.split_k)
         torch.cuda.synchronize()
-        status = self.fl.consume_status()
-        assert status == 0, f"kernel status word {status:#x}"
+        if check_status:
+            status = self.fl.consume_status()
+            assert status == 0, f"kernel status word {status:#x}"
         return self.C.cpu().numpy()
 
 

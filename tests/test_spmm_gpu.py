@@ -78,7 +78,8 @@ def test_workspace_split_k(lib, oracle, split_k, workspace_k, cluster_k):
                                   dict(chunk_vectors=512, ring_slots=6, producers=2),
                                   dict(chunk_vectors=1024, ring_slots=3, a_stages=4)])
 def test_pipeline_shapes(lib, oracle, plan):
-    _run_case(lib, oracle, 256, 1536, 16, 0.7, plan=dict(cluster_k=2, **plan))
+    """Pipeline depths, ring geometries and producer counts of the ring form of the kernel."""
+    _run_case(lib, oracle, 256, 1536, 16, 0.7, plan=dict(path=1, cluster_k=2, **plan))
 
 
 @pytest.mark.parametrize("sparsity", [0.0, 0.3, 0.5, 0.95, 0.999, 1.0])

@@ -1,0 +1,120 @@
+"""Both forms of the SpMM kernel against the CPU oracle, whichever of them the automatic plan prefers: the ring form
+(bulk copies of the compressed stream into shared memory) and the register-streaming form (global loads into the
+scatter warps' registers).  Calls go through the C ABI of libSpMM_API.so."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import DeviceProblem, assert_close, random_problem
+
+pytestmark = pytest.mark.gpu
+
+FORMS = [dict(path=1), dict(path=2, scatter_warps=8), dict(path=2, scatter_warps=4)]
+FORM_IDS = ["ring", "direct8", "direct4"]
+
+
+def _check(lib, oracle, A, B, N, split_k, plan, note):
+    M, K = A.shape
+    comp, offs, _ = lib.InitSparseMatrixA_API(A)
+    want = oracle.gemm_f32(A, B)
+    lib.set_plan(**plan)
+    try:
+        got = DeviceProblem(lib, comp, offs, B, M, N, K, split_k).run()
+        used = lib.get_plan(M, N, K, split_k)
+    finally:
+        lib.set_plan()
+    assert used["path"] == plan["path"]
+    assert_close(got, want, f"{note} plan={plan}")
+    return got
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+@pytest.mark.parametrize("N", [8, 16, 32, 64, 128])
+def test_every_n_tile(lib, oracle, form, N):
+    A, B = random_problem(lib, 384, 1024, N, 0.8, 100 + N)
+    _check(lib, oracle, A, B, N, 1, dict(cluster_k=1, **form), f"N={N}")
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+@pytest.mark.parametrize("sparsity", [0.0, 0.3, 0.6, 0.7, 0.75, 0.95, 0.999, 1.0])
+def test_densities(lib, oracle, form, sparsity):
+    """From fully dense tiles (2048 vectors, far beyond what the register-streaming form keeps in registers) through
+    the densities around its register budget (512 and 768 vectors per tile) down to empty tiles."""
+    A, B = random_problem(lib, 256, 1536, 16, sparsity, 7)
+    _check(lib, oracle, A, B, 16, 1, dict(cluster_k=1, **form), f"s={sparsity}")
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+def test_dense_and_sparse_tiles_alternate_in_a_stage(lib, oracle, form):
+    """Successive tiles of one stage switch between tiles above the register budget of the register-streaming form,
+    tiles within it and empty tiles, in every order."""
+    M, K, N = 256, 64 * 48, 16
+    rng = np.random.default_rng(11)
+    A = np.zeros((M, K), np.float16)
+    density = rng.choice([0.0, 0.02, 0.2, 0.3, 0.45, 1.0], size=(M // 128, K // 64))
+    for r in range(M // 128):
+        for c in range(K // 64):
+            tile = rng.uniform(-1, 1, (128, 64)).astype(np.float16)
+            tile[tile == 0] = np.float16(0.5)
+            tile[rng.random((128, 64)) >= density[r, c]] = 0
+            A[r * 128:(r + 1) * 128, c * 64:(c + 1) * 64] = tile
+    B = lib.synthetic.dense_uniform_matrix(N, K, 12).numpy()
+    _check(lib, oracle, A, B, N, 1, dict(cluster_k=1, **form), "alternating densities")
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+@pytest.mark.parametrize("cluster_k,workspace_k,split_k", [(2, 1, 1), (4, 1, 1), (1, 3, 6), (2, 2, 4), (8, 1, 1)])
+def test_k_splits(lib, oracle, form, cluster_k, workspace_k, split_k):
+    A, B = random_problem(lib, 256, 2048, 16, 0.8, 13)
+    _check(lib, oracle, A, B, 16, split_k, dict(cluster_k=cluster_k, workspace_k=workspace_k, **form), "K split")
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+def test_fewer_tiles_than_scatter_warps(lib, oracle, form):
+    for k_tiles in (1, 2, 3, 5, 9):
+        A, B = random_problem(lib, 128, 64 * k_tiles, 16, 0.8, 20 + k_tiles)
+        _check(lib, oracle, A, B, 16, 1, dict(cluster_k=1, **form), f"{k_tiles} K tiles")
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+def test_forms_agree(lib, oracle, form):
+    """The forms differ in how words reach the stage and in how many accumulators the tiles are dealt to (the
+    register-streaming form keeps one per MMA-issuing thread and adds them at the end), so results agree to fp32
+    summation order."""
+    M, K, N = 1024, 4096, 32
+    A, B = random_problem(lib, M, K, N, 0.8, 31)
+    comp, offs, _ = lib.InitSparseMatrixA_API(A)
+    prob = DeviceProblem(lib, comp, offs, B, M, N, K, 1)
+    results = []
+    for plan in (dict(path=1, cluster_k=2), dict(cluster_k=2, **form)):
+        lib.set_plan(**plan)
+        try:
+            results.append(prob.run().copy())
+        finally:
+            lib.set_plan()
+    assert_close(results[1], results[0].astype(np.float32), f"{form} against the ring form")
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+def test_malformed_offsets_are_reported_not_followed(lib, form):
+    """A TileOffsets entry that runs backwards makes the kernel give up with status bit 2 instead of reading there."""
+    M, K, N = 256, 1024, 16
+    A, B = random_problem(lib, M, K, N, 0.8, 41)
+    comp, offs, _ = lib.InitSparseMatrixA_API(A)
+    offs = offs.copy()
+    offs[5] = offs[4] - 3
+    lib.set_plan(cluster_k=1, **form)
+    try:
+        DeviceProblem(lib, comp, offs, B, M, N, K, 1).run(check_status=False)
+        status = lib.consume_status()
+    finally:
+        lib.set_plan()
+    assert status & 2
+    # the library keeps working afterwards
+    comp, offs, _ = lib.InitSparseMatrixA_API(A)
+    torch.cuda.synchronize()
+    lib.set_plan(cluster_k=1, **form)
+    try:
+        DeviceProblem(lib, comp, offs, B, M, N, K, 1).run()
+    finally:
+        lib.set_plan()

@@ -29,26 +29,31 @@ def _device_problem(lib, M, K, N, sparsity, seed):
 def test_no_alloc_entry_matches_workspace_entry(lib, oracle, M, K, N, split_k):
     A, B, comp_d, offs_d, B_d = _device_problem(lib, M, K, N, 0.8, seed=7 + N)
     stream = torch.cuda.current_stream().cuda_stream
-    plan = lib.get_plan(M, N, K, split_k)
-    if split_k > 1:
-        assert plan["workspace_k"] > 1, "this case is meant to exercise the scratch"
-    want = torch.full((N, M), float("nan"), dtype=torch.float16, device="cuda")
-    ws = torch.empty((split_k, N, M), dtype=torch.float16, device="cuda")
-    lib.SpMM_SplitK_API(stream, None, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), want.data_ptr(), M, N, K,
-                        ws.data_ptr(), split_k)
-    torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
-    for call in range(2):  # the second call finds the first call's partial sums in the scratch
-        got = torch.full((N, M), float("nan"), dtype=torch.float16, device="cuda")
-        base = torch.cuda.memory_allocated()
-        lib.spmm_splitk_no_alloc(stream, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), got.data_ptr(), M, N, K,
-                                 split_k)
+    if split_k > 1:  # problems this small would be cut inside clusters: pin the cut that goes through the scratch
+        lib.set_plan(cluster_k=1, workspace_k=split_k // 2)
+    try:
+        plan = lib.get_plan(M, N, K, split_k)
+        if split_k > 1:
+            assert plan["workspace_k"] > 1, "this case is meant to exercise the scratch"
+        want = torch.full((N, M), float("nan"), dtype=torch.float16, device="cuda")
+        ws = torch.empty((split_k, N, M), dtype=torch.float16, device="cuda")
+        lib.SpMM_SplitK_API(stream, None, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), want.data_ptr(), M, N, K,
+                            ws.data_ptr(), split_k)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == base
-        assert lib.consume_status() == 0
-        assert_close(got.cpu().numpy(), want.cpu().numpy().astype(np.float32), f"no-alloc call {call}")
-        assert_close(got.cpu().numpy(), oracle.gemm_f32(A, B), f"no-alloc call {call} vs host GEMM")
-    assert before <= torch.cuda.memory_allocated()
+        before = torch.cuda.memory_allocated()
+        for call in range(2):  # the second call finds the first call's partial sums in the scratch
+            got = torch.full((N, M), float("nan"), dtype=torch.float16, device="cuda")
+            base = torch.cuda.memory_allocated()
+            lib.spmm_splitk_no_alloc(stream, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), got.data_ptr(), M, N,
+                                     K, split_k)
+            torch.cuda.synchronize()
+            assert torch.cuda.memory_allocated() == base
+            assert lib.consume_status() == 0
+            assert_close(got.cpu().numpy(), want.cpu().numpy().astype(np.float32), f"no-alloc call {call}")
+            assert_close(got.cpu().numpy(), oracle.gemm_f32(A, B), f"no-alloc call {call} vs host GEMM")
+        assert before <= torch.cuda.memory_allocated()
+    finally:
+        lib.set_plan()
 
 
 def test_no_alloc_entry_refuses_oversized_requests(lib, capfd):
