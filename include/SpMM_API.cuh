@@ -29,10 +29,10 @@
  * All pointers are device pointers.  `A` is never read (callers pass nullptr).  Enqueues on `stream` and
  * returns without synchronising.  N must be 8, 16, 32, 64 or a multiple of 128 (otherwise the reference's
  * message is printed and cudaErrorUnknown returned); M % 128 == 0 and K % 64 == 0 (the reference kernel needs
- * M % 256 == 0 for N <= 32; this one does not).  Split_K >= 1 is a hint: the kernel always splits K inside
- * thread-block clusters and sums the parts in fp32 through distributed shared memory; when that alone does not
- * fill the GPU it also parks up to Split_K/2 fp32 partial matrices in Reduction_Workspace (>= Split_K*M*N halves,
- * 16-byte aligned; may be nullptr when Split_K == 1) and rounds to fp16 once, after summing them. */
+ * M % 256 == 0 for N <= 32; this one does not).  Split_K >= 1 is a hint: K is cut only as far as it takes to fill
+ * the GPU, into up to Split_K/2 parts whose fp32 partial matrices are parked in Reduction_Workspace (>= Split_K*M*N
+ * halves, 16-byte aligned; may be nullptr when Split_K == 1) and summed by a second kernel that rounds to fp16 once,
+ * and/or into parts of a thread-block cluster that are summed in fp32 through distributed shared memory. */
 cudaError_t SpMM_SplitK_API(cudaStream_t stream,
                             const half*  A,
                             const uint4* Compressed_A,
@@ -145,19 +145,23 @@ void FlashLLM_SetLaunchOverlap(int enable);
 
 /* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
  * csrc/SpMM_API.cu:79-118): fixes launch-plan fields for subsequent calls from this process.  `fields` holds up to
- * nine ints, 0 = choose automatically, in this order:
+ * ten ints, 0 = choose automatically, in this order:
  *   0 cluster_k       K parts summed inside a thread-block cluster through distributed shared memory (1..8)
  *   1 workspace_k     extra K parts through Reduction_Workspace (capped at Split_K/2 of the call: an fp32 partial
  *                     matrix takes the room of two fp16 ones)
  *   2 a_stages        decompressed 128x64 tiles in flight        3 b_stages  B batches in flight
  *   4 b_batch         K tiles of B per TMA instruction
- *   5 ring_slots x 6 chunk_vectors (16 bytes each, power of two): the compressed-stream ring
- *   7 scatter_warps   warps that decompress tiles, one whole tile per warp at a time (4..12, at most a_stages)
- *   8 producers       warps issuing the bulk copies (1..4; must divide ring_slots)
+ *   5 ring_slots x 6 chunk_vectors (16 bytes each, power of two): the compressed-stream ring (ring form only)
+ *   7 scatter_warps   warps that decompress tiles, one whole tile per warp at a time (ring form: 4..12, at most
+ *                     a_stages; register-streaming form: 4, two CTAs per SM, or 8, one CTA per SM)
+ *   8 producers       warps issuing the bulk copies (ring form only: 1..4; must divide ring_slots)
+ *   9 path            1 = ring form: the compressed stream is copied into a shared-memory ring by bulk copies;
+ *                     2 = register-streaming form (the default): scatter warps load their tiles' words from global
+ *                     memory into registers, tiles alternate between two MMA-issuing threads
  * FlashLLM_SetPlan(nullptr, 0) restores automatic choice. */
 void FlashLLM_SetPlan(const int* fields, int count);
 
-/* Describes the plan the next SpMM call with these sizes would use: out[0..8] as above, out[9] = dynamic shared
+/* Describes the plan the next SpMM call with these sizes would use: out[0..9] as above, out[10] = dynamic shared
  * memory in bytes; `count` = entries available in `out`. */
 int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count);
 
