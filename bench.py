@@ -192,6 +192,7 @@ def cpu_baseline(sample_seconds: float = 12.0) -> dict:
     from oracle import cpu_oracle
     name, M, K, _, _ = OPT66B_LAYER[2]
     cores = os.cpu_count() or 1
+    cpu_oracle.set_threads(cores)  # torch.distributed.run pins OMP_NUM_THREADS=1 in the ranks' environment
     rows = 1024
     A = fl.synthetic.sparse_uniform_matrix(M, K, SPARSITY, SEED + 2, rows=(0, rows)).numpy()
     B = fl.synthetic.dense_uniform_matrix(N_TOKENS, K, (SEED + 2) ^ 0xB).numpy()

@@ -97,6 +97,11 @@ def decode(comp: np.ndarray, offs: np.ndarray, M: int, K: int) -> np.ndarray:
     return out
 
 
+def set_threads(n: int) -> None:
+    """Host threads used by the OpenMP loops of the oracle (overrides an OMP_NUM_THREADS pinned by a launcher)."""
+    lib().oracle_set_threads(int(n))
+
+
 def gemm_f32(A: np.ndarray, B: np.ndarray, rows: tuple[int, int] | None = None, timed: bool = False) -> np.ndarray:
     """C[N][M] float32 = B[N][K] @ A[M][K]^T on the host; ``rows`` limits the computed A rows."""
     A, B = _as_u16(A), _as_u16(B)

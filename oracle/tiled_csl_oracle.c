@@ -306,6 +306,22 @@ void oracle_decode(const uint32_t* Compressed_A, const int* TileOffsets, int M, 
 
 /* ---------------------------------------------------------------- host dense GEMM */
 
+/* Number of host threads the OpenMP loops below use.  A launcher may have pinned OMP_NUM_THREADS to 1 in the
+ * environment (torch.distributed.run does); callers that time the host path on all cores set it back here. */
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+void oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+
 /* C[n][m] = sum_k float(A[m][k]) * float(B[n][k]); rows [m_begin, m_end) only, double accumulation,
  * result stored as float.  A row-major [M][K], B row-major [N][K], C row-major [N][M]. */
 void oracle_gemm_f32(const uint16_t* A, const uint16_t* B, float* C, int M, int N, int K, int m_begin, int m_end)
