@@ -17,6 +17,8 @@ overlap one another), `roofline` of the dominant kernel (FFN1-shaped
 SpMM, algorithmic bytes / CUDA-event time against the measured HBM copy bandwidth) and `cpu_baseline` (host fp32
 dense GEMM of the oracle on a bounded row sample, all host threads).
 
+--workload tp-chain     runs the tensor-parallel layer chain instead (column-parallel QKV/FFN1, row-parallel
+                        out-proj/FFN2, NCCL all-reduce after each row-parallel SpMM), checked against the host layer.
 --impl reference        times that CPU path alone (reference host encoder + host dense GEMM), rank 0 only.
 --impl reference-gpu    times the unmodified reference CUDA kernel (built from its own sources) on the same inputs.
 """
@@ -411,6 +413,105 @@ def run_reference_gpu(args) -> None:
                       "per_shape": per_shape}), flush=True)
 
 
+def run_tp_chain(args) -> None:
+    """BASELINE config 5: the tensor-parallel sparse layer chain at OPT-66B dimensions.  QKV and FFN1 are
+    column-parallel, out-proj and FFN2 row-parallel over the ranks, with an NCCL all-reduce of [N][H] fp16 after each
+    row-parallel SpMM; weights N(0, 0.02) magnitude-pruned to 80 % per matrix, activations N(0, 1), N = 16."""
+    import flash_llm_b200 as fl
+    from flash_llm_b200 import tp_chain
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    fl.library()
+    H, F = 9216, 36864
+    shape = tp_chain.ChainShape(hidden=H, ffn=F, tokens=N_TOKENS, world=world)
+    seed = SEED + 0x50
+    full = [fl.synthetic.magnitude_pruned_matrix(m, k, SPARSITY, 0.02, seed + i, device=dev)
+            for i, (m, k) in enumerate(((3 * H, H), (H, H), (F, H), (H, F)))]
+    shards = tp_chain.shard_weights(shape, rank, *full)
+    chain = tp_chain.DeviceChain(fl, shape, shards, dev, split_k=8)
+    x = fl.synthetic.normal_matrix(N_TOKENS, H, 1.0, seed + 9, device=dev).to(torch.float16)
+    fl.set_launch_overlap(True)
+
+    def all_reduce(t):
+        if world > 1:
+            dist.all_reduce(t)
+        return t
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- parity of the sharded chain over the real collective against the unsharded layer on the host (rank 0)
+    out = chain.step(x, all_reduce).clone()
+    torch.cuda.synchronize(dev)
+    status = fl.consume_status()
+    assert status == 0, f"kernel status {status:#x}"
+    parity = None
+    if rank == 0:
+        want = tp_chain.reference_chain(shape, x.cpu(), *[w.cpu() for w in full])
+        got = out.cpu().float()
+        rms = float(want.pow(2).mean().sqrt())
+        rel = float(((got - want).abs() / want.abs().clamp_min(0.05 * rms)).max())
+        parity = {"max_rel_err_floor_5pct_rms": rel, "max_abs_over_peak": float((got - want).abs().max() / want.abs().max())}
+    del full
+
+    for _ in range(max(args.warmup, 3)):
+        chain.step(x, all_reduce)
+    barrier()
+    launches_before = fl.launch_count()
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        t_begin = time.time()
+        ms = time_loop(lambda: chain.step(x, all_reduce), args.steps, dev)
+        clocks.mark(t_begin, time.time())
+        time.sleep(0.05)
+    launches = fl.launch_count() - launches_before
+    barrier()
+    ms = max_over_ranks(ms)
+    # the same kernels without the collectives (every rank on its own partial sums), and the collective on its own
+    ms_local = max_over_ranks(time_loop(lambda: chain.step(x, lambda t: t), args.steps, dev))
+    buf = torch.zeros((N_TOKENS, H), dtype=torch.float16, device=dev)
+    barrier()
+    ms_coll = max_over_ranks(time_loop(lambda: all_reduce(buf), args.steps, dev)) if world > 1 else 0.0
+    status = fl.consume_status()
+    assert status == 0, f"kernel status {status:#x}"
+    if rank == 0:
+        bytes_alg = sum(l["bytes_alg"] for l in chain.layers.values())
+        print(json.dumps({
+            "metric": "spmm_effective_tflops", "value": shape.flops() * args.steps / (ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "tensor-parallel sparse layer chain, OPT-66B dimensions (H=9216, F=36864), N=16, "
+                                   "N(0,0.02) weights magnitude-pruned to 80 % per matrix, activations N(0,1): QKV -> "
+                                   "out-proj -> all-reduce -> FFN1 -> ReLU -> FFN2 -> all-reduce",
+                       "parallelism": f"tp{world}: QKV/FFN1 column-parallel, out-proj/FFN2 row-parallel, NCCL all-reduce "
+                                      f"of {N_TOKENS}x{H} fp16 after each row-parallel SpMM",
+                       "shards": {k: list(v) for k, v in shape.shard_shapes().items()}},
+            "ms_per_step_without_collectives": ms_local / args.steps,
+            "ms_per_all_reduce_alone": ms_coll / args.steps,
+            "hbm_gbs_per_gpu": bytes_alg * args.steps / (ms * 1e-3) / 1e9,
+            "parity_vs_host_layer": parity, "gpu_launches": launches, "clocks": clocks.summary()}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -418,8 +519,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="layer", choices=["layer", "tp-chain"],
+                    help="layer: the four OPT-66B SpMMs, weight rows sharded, no collective (the headline metric); "
+                         "tp-chain: the tensor-parallel layer chain with NCCL all-reduces")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "tp-chain" and args.impl == "ours":
+        run_tp_chain(args)
+    elif args.impl == "reference":
         run_reference_cpu(args)
     elif args.impl == "reference-gpu":
         run_reference_gpu(args)
