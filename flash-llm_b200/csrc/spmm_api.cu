@@ -26,6 +26,13 @@ __device__ unsigned int g_status_word = 0;
 constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
+// Arrival counters of the launches whose last CTA per output tile sums the workspace parts itself.  All zero between
+// launches (the last arrival resets its counter).  Consecutive calls take consecutive regions, so that calls running
+// at the same time on different streams do not share counters unless more than kCounterRegions are in flight.
+constexpr int kCounterRegions = 32, kCountersPerRegion = 8192;
+static __device__ unsigned int g_tile_counters[kCounterRegions * kCountersPerRegion];
+static std::atomic<unsigned int> g_counter_region{0};
+
 static std::atomic<unsigned long long> g_launches{0};
 
 void count_launch()
@@ -44,6 +51,7 @@ struct DeviceState {
     int            smem_optin = 0;
     unsigned int*  status     = nullptr;
     unsigned char* noalloc_scratch = nullptr;  // device address of g_noalloc_scratch on this device
+    unsigned int*  tile_counters   = nullptr;  // device address of g_tile_counters on this device
 };
 
 static DeviceState g_devices[kMaxDevices];
@@ -104,6 +112,8 @@ static DeviceState* device_state(cudaError_t* err)
             e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->status), g_status_word);
         if (e == cudaSuccess)
             e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->noalloc_scratch), g_noalloc_scratch);
+        if (e == cudaSuccess)
+            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->tile_counters), g_tile_counters);
         // The opt-in limit is a per-device property of each kernel; raise it once instead of on every call
         // (the reference calls cudaFuncSetAttribute per launch, csrc/SpMM_API.cu:36-37).
         if (e == cudaSuccess)
@@ -151,6 +161,7 @@ static PlanOverride g_override;
 static std::mutex   g_override_mutex;
 static std::atomic<int> g_launch_overlap{0};
 
+
 constexpr int kDefaultPath = kPathDirect;
 
 static int n_tile_for(int N)
@@ -191,6 +202,9 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // Two pipelines per SM (4 scatter warps, 4 stages each) where they fit; wide-N tiles need the shared memory for
     // their B batches, so they run one deeper pipeline per SM instead.
     pl.path               = ov.v[kPlanPath] ? ov.v[kPlanPath] : kDefaultPath;
+    // default: the second kernel; measured faster than the last-CTA sum on every benchmark shape (it overlaps the SpMM
+    // kernel's tail under launch overlap, while the last CTA of a tile sums with 128 threads at the very end)
+    pl.reduction          = ov.v[kPlanReduction] ? ov.v[kPlanReduction] : kReduceSecondKernel;
     const bool direct     = pl.path == kPathDirect;
     pl.scatter_warps      = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps]
                                                     : (direct ? (pl.n_tile <= 64 ? 4 : 8) : (pl.n_tile <= 32 ? 4 : 8));
@@ -257,6 +271,9 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     if ((static_cast<long long>(M) * N) % 4 != 0)
         extra = 1;  // the workspace reduction moves four values per thread
     pl.workspace_k = extra;
+    if (!direct || pl.cluster_k != 1 || pl.workspace_k == 1
+        || static_cast<long long>(tile_rows) * n_tiles > kCountersPerRegion)
+        pl.reduction = kReduceSecondKernel;
     // room for this CTA's slice of TileOffsets (K tiles of the longest part, plus one), up to 8 KB
     const int longest = (k_tiles + pl.cluster_k * pl.workspace_k - 1) / (pl.cluster_k * pl.workspace_k) + 1;
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
@@ -273,6 +290,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     const bool direct_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8)
                            && pl.a_stages == pl.scatter_warps && pl.b_batch % kDirectIssuers == 0;
     const bool ok = (pl.path == kPathRing || pl.path == kPathDirect) && (direct ? direct_ok : ring_ok)
+                    && (pl.reduction == kReduceSecondKernel || pl.reduction == kReduceLastCta)
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
                     && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
@@ -400,6 +418,7 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     params.out          = C;
     params.partial      = pl.workspace_k > 1 ? reinterpret_cast<float*>(Reduction_Workspace) : nullptr;
     params.status       = st->status;
+    params.counters     = nullptr;
     params.M            = M_Global;
     params.N            = N_Global;
     params.K            = K_Global;
@@ -422,6 +441,14 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
 
     const int tile_rows = M_Global / kTileM;
     const int n_tiles   = (N_Global + pl.n_tile - 1) / pl.n_tile;
+    // Workspace parts of the register-streaming form are summed by the last CTA of every output tile when the launch
+    // has no clusters and its tiles fit one counter region; otherwise by a second kernel.
+    const bool fused_reduction = pl.path == kPathDirect && pl.workspace_k > 1 && pl.cluster_k == 1
+                                 && pl.reduction == kReduceLastCta;
+    if (fused_reduction)
+        params.counters = st->tile_counters
+                          + static_cast<size_t>(g_counter_region.fetch_add(1, std::memory_order_relaxed) % kCounterRegions)
+                                * kCountersPerRegion;
     switch (pl.n_tile) {
         case 16: err = launch_spmm<16>(stream, tmap, params, tile_rows, n_tiles); break;
         case 32: err = launch_spmm<32>(stream, tmap, params, tile_rows, n_tiles); break;
@@ -430,7 +457,7 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     }
     if (err != cudaSuccess)
         return err;
-    if (pl.workspace_k > 1)
+    if (pl.workspace_k > 1 && !fused_reduction)
         return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k);
     return cudaSuccess;
 }
@@ -527,7 +554,7 @@ int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count)
         return static_cast<int>(err);
     const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k,   pl.a_stages,      pl.b_stages,  pl.b_batch,
                                              pl.ring_slots, pl.chunk_vectors, pl.scatter_warps, pl.producers, pl.path,
-                                             pl.smem_bytes};
+                                             pl.reduction,  pl.smem_bytes};
     for (int i = 0; i < count && i <= kPlanFieldCount; ++i)
         out[i] = values[i];
     return 0;
