@@ -43,8 +43,8 @@ import torch  # noqa: E402
 # (name, M, K, Split_K given to this library, Split_K of the reference's own table).  This library treats Split_K as an
 # upper bound (it sizes the workspace) and cuts K only as far as filling the GPU takes, so one generous value serves
 # every shard size; the reference cuts exactly Split_K ways (kernel_benchmark/benchmark.sh:13-15, tuned there).
-OPT66B_LAYER = [("qkv", 27648, 9216, 16, 2), ("out_proj", 9216, 9216, 16, 6), ("ffn1", 36864, 9216, 16, 3),
-                ("ffn2", 9216, 36864, 16, 6)]
+OPT66B_LAYER = [("qkv", 27648, 9216, 64, 2), ("out_proj", 9216, 9216, 64, 6), ("ffn1", 36864, 9216, 64, 3),
+                ("ffn2", 9216, 36864, 64, 6)]
 N_TOKENS = 16
 SPARSITY = 0.8
 SEED = 0xF1A50000
@@ -254,7 +254,7 @@ def cpu_baseline(sample_seconds: float = 12.0) -> dict:
 
 def config_dict(world: int) -> dict:
     return {"workload": "OPT-66B decoder-layer SpMMs (27648x9216, 9216x9216, 36864x9216, 9216x36864), N=16 tokens, "
-                        "80% uniform-random sparsity, fp16, tiled-CSL, Split_K tuned per shape (ours: upper bound 16, the plan decides; reference 2/6/3/6)",
+                        "80% uniform-random sparsity, fp16, tiled-CSL, Split_K tuned per shape (ours: upper bound 64, the plan decides; reference 2/6/3/6)",
             "sharding": f"weight rows split evenly over {world} GPU(s), no collective",
             "l2": "inputs larger than L2: each step streams ~821 MB of compressed weights (126 MB L2)",
             "tokens": N_TOKENS, "sparsity": SPARSITY,
@@ -440,7 +440,7 @@ def run_tp_chain(args) -> None:
     full = [fl.synthetic.magnitude_pruned_matrix(m, k, SPARSITY, 0.02, seed + i, device=dev)
             for i, (m, k) in enumerate(((3 * H, H), (H, H), (F, H), (H, F)))]
     shards = tp_chain.shard_weights(shape, rank, *full)
-    chain = tp_chain.DeviceChain(fl, shape, shards, dev, split_k=8)
+    chain = tp_chain.DeviceChain(fl, shape, shards, dev, split_k=64)
     x = fl.synthetic.normal_matrix(N_TOKENS, H, 1.0, seed + 9, device=dev).to(torch.float16)
     fl.set_launch_overlap(True)
 

@@ -26,13 +26,6 @@ __device__ unsigned int g_status_word = 0;
 constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
-// Arrival counters of the launches whose last CTA per output tile sums the workspace parts itself.  All zero between
-// launches (the last arrival resets its counter).  Consecutive calls take consecutive regions, so that calls running
-// at the same time on different streams do not share counters unless more than kCounterRegions are in flight.
-constexpr int kCounterRegions = 32, kCountersPerRegion = 8192;
-static __device__ unsigned int g_tile_counters[kCounterRegions * kCountersPerRegion];
-static std::atomic<unsigned int> g_counter_region{0};
-
 static std::atomic<unsigned long long> g_launches{0};
 
 void count_launch()
@@ -51,7 +44,6 @@ struct DeviceState {
     int            smem_optin = 0;
     unsigned int*  status     = nullptr;
     unsigned char* noalloc_scratch = nullptr;  // device address of g_noalloc_scratch on this device
-    unsigned int*  tile_counters   = nullptr;  // device address of g_tile_counters on this device
 };
 
 static DeviceState g_devices[kMaxDevices];
@@ -112,8 +104,6 @@ static DeviceState* device_state(cudaError_t* err)
             e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->status), g_status_word);
         if (e == cudaSuccess)
             e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->noalloc_scratch), g_noalloc_scratch);
-        if (e == cudaSuccess)
-            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->tile_counters), g_tile_counters);
         // The opt-in limit is a per-device property of each kernel; raise it once instead of on every call
         // (the reference calls cudaFuncSetAttribute per launch, csrc/SpMM_API.cu:36-37).
         if (e == cudaSuccess)
@@ -202,9 +192,6 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // Two pipelines per SM (4 scatter warps, 4 stages each) where they fit; wide-N tiles need the shared memory for
     // their B batches, so they run one deeper pipeline per SM instead.
     pl.path               = ov.v[kPlanPath] ? ov.v[kPlanPath] : kDefaultPath;
-    // default: the second kernel; measured faster than the last-CTA sum on every benchmark shape (it overlaps the SpMM
-    // kernel's tail under launch overlap, while the last CTA of a tile sums with 128 threads at the very end)
-    pl.reduction          = ov.v[kPlanReduction] ? ov.v[kPlanReduction] : kReduceSecondKernel;
     const bool direct     = pl.path == kPathDirect;
     pl.scatter_warps      = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps]
                                                     : (direct ? (pl.n_tile <= 64 ? 4 : 8) : (pl.n_tile <= 32 ? 4 : 8));
@@ -227,27 +214,29 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
         pl.chunk_vectors = 0;
     }
 
-    // How to cut K.  A CTA that owns a whole tile row needs no reduction and pays its pipeline fill once, so K is cut
-    // only to fill the GPU: with `slots` CTAs resident at a time, G parts per tile row run in ceil(rows*G/slots)
-    // waves, and the best G is the one whose last wave is fullest (measured on 216 tile rows and 296 slots: 2, 3 parts
-    // gain nothing, 4 parts +8 %).  Parts that go through the caller's workspace (fp32 partial matrices summed by a
-    // second kernel; at most Split_K/2 of them) are cheaper than parts of a thread-block cluster (summed through
-    // distributed shared memory, CTAs co-scheduled) except on small problems, where the second launch costs more than
-    // it saves; clusters also take what the workspace cannot.  Replaces the reference's hand-tuned Split_K tables
-    // (kernel_benchmark/benchmark.sh:13-15).
+    // How to cut K.  A CTA that owns a whole tile row needs no reduction and pays its set-up and pipeline fill once,
+    // so K is cut only to fill the GPU.  With `slots` CTAs resident at a time, G workspace parts per tile row run in
+    // ceil(rows*G/slots) waves of CTAs that each process k_tiles/G tiles after a fixed cost worth about 16 tiles, and
+    // the second kernel adds about half a tile's time per part; the G with the smallest total wins.  (Fitted to
+    // measurements: 216 tile rows on 296 slots gain nothing from 2 or 3 parts and 8 % from 4; 9 tile rows of 576
+    // K tiles run 39 / 25 / 23 us with 8 / 16 / 32 parts.)  Parts that go through the caller's workspace (fp32 partial
+    // matrices; at most Split_K/2 of them) are cheaper than parts of a thread-block cluster (summed through
+    // distributed shared memory, CTAs co-scheduled) except on small problems, where the second launch costs more
+    // than it saves; clusters also take what the workspace cannot.  Replaces the reference's hand-tuned Split_K
+    // tables (kernel_benchmark/benchmark.sh:13-15).
     const int slots     = st->sm_count * (two_per_sm ? 2 : 1);
     const int max_extra = ((static_cast<long long>(M) * N) % 4 != 0) ? 1 : (Split_K / 2 > 1 ? Split_K / 2 : 1);
     const bool small    = static_cast<long long>(tile_rows) * k_tiles <= 4096;
     int        best_s = 1, best_g = 1;
     if (!small) {
-        double best_score = -1.0;
-        for (int g = 1; g <= max_extra && g <= 8 && g <= k_tiles; ++g) {
-            const double x     = static_cast<double>(ctas_flat) * g / slots;
-            const double waves = static_cast<double>(static_cast<long long>(x + 0.999999));
-            const double score = x / waves - 0.015 * (g - 1);
-            if (score > best_score) {
-                best_score = score;
-                best_g     = g;
+        double best_cost = 0.0;
+        for (int g = 1; g <= max_extra && g <= 32 && g <= k_tiles; ++g) {
+            const long long ctas  = static_cast<long long>(ctas_flat) * g;
+            const double    waves = static_cast<double>((ctas + slots - 1) / slots);
+            const double    cost  = waves * (static_cast<double>(k_tiles) / g + 16.0) + (g > 1 ? 0.5 * g : 0.0);
+            if (g == 1 || cost < best_cost) {
+                best_cost = cost;
+                best_g    = g;
             }
         }
     }
@@ -271,9 +260,6 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     if ((static_cast<long long>(M) * N) % 4 != 0)
         extra = 1;  // the workspace reduction moves four values per thread
     pl.workspace_k = extra;
-    if (!direct || pl.cluster_k != 1 || pl.workspace_k == 1
-        || static_cast<long long>(tile_rows) * n_tiles > kCountersPerRegion)
-        pl.reduction = kReduceSecondKernel;
     // room for this CTA's slice of TileOffsets (K tiles of the longest part, plus one), up to 8 KB
     const int longest = (k_tiles + pl.cluster_k * pl.workspace_k - 1) / (pl.cluster_k * pl.workspace_k) + 1;
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
@@ -290,7 +276,6 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     const bool direct_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8)
                            && pl.a_stages == pl.scatter_warps && pl.b_batch % kDirectIssuers == 0;
     const bool ok = (pl.path == kPathRing || pl.path == kPathDirect) && (direct ? direct_ok : ring_ok)
-                    && (pl.reduction == kReduceSecondKernel || pl.reduction == kReduceLastCta)
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
                     && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
@@ -418,7 +403,6 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     params.out          = C;
     params.partial      = pl.workspace_k > 1 ? reinterpret_cast<float*>(Reduction_Workspace) : nullptr;
     params.status       = st->status;
-    params.counters     = nullptr;
     params.M            = M_Global;
     params.N            = N_Global;
     params.K            = K_Global;
@@ -441,14 +425,6 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
 
     const int tile_rows = M_Global / kTileM;
     const int n_tiles   = (N_Global + pl.n_tile - 1) / pl.n_tile;
-    // Workspace parts of the register-streaming form are summed by the last CTA of every output tile when the launch
-    // has no clusters and its tiles fit one counter region; otherwise by a second kernel.
-    const bool fused_reduction = pl.path == kPathDirect && pl.workspace_k > 1 && pl.cluster_k == 1
-                                 && pl.reduction == kReduceLastCta;
-    if (fused_reduction)
-        params.counters = st->tile_counters
-                          + static_cast<size_t>(g_counter_region.fetch_add(1, std::memory_order_relaxed) % kCounterRegions)
-                                * kCountersPerRegion;
     switch (pl.n_tile) {
         case 16: err = launch_spmm<16>(stream, tmap, params, tile_rows, n_tiles); break;
         case 32: err = launch_spmm<32>(stream, tmap, params, tile_rows, n_tiles); break;
@@ -457,7 +433,7 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     }
     if (err != cudaSuccess)
         return err;
-    if (pl.workspace_k > 1 && !fused_reduction)
+    if (pl.workspace_k > 1)
         return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k);
     return cudaSuccess;
 }
@@ -554,7 +530,7 @@ int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count)
         return static_cast<int>(err);
     const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k,   pl.a_stages,      pl.b_stages,  pl.b_batch,
                                              pl.ring_slots, pl.chunk_vectors, pl.scatter_warps, pl.producers, pl.path,
-                                             pl.reduction,  pl.smem_bytes};
+                                             pl.smem_bytes};
     for (int i = 0; i < count && i <= kPlanFieldCount; ++i)
         out[i] = values[i];
     return 0;

@@ -108,7 +108,6 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     const uint32_t misc_off = (acc_full + 8u) - base;
     volatile uint32_t* const tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem + misc_off);
     volatile uint32_t* const abort_flag = reinterpret_cast<volatile uint32_t*>(smem + misc_off + 4);
-    volatile uint32_t* const last_flag  = reinterpret_cast<volatile uint32_t*>(smem + misc_off + 8);
     int* const               offs_stage = reinterpret_cast<int*>(smem + misc_off + 16);  // plan.offsets_staged ints
 
     // ---- work assignment: blockIdx.x = K part inside the cluster, y = tile row, z = (N tile, workspace part)
@@ -126,14 +125,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     const int* const offs        = staged ? offs_stage : offs_global;  // valid after the set-up barrier
 
     if (raw_addr != base) {  // the launch did not honour the 1024-byte alignment: nothing below would be valid
-        if (threadIdx.x == 0) {
+        if (threadIdx.x == 0)
             atomicOr(p.status, kStatusSmemMisaligned);
-            if (p.counters != nullptr) {  // keep the arrival counters consistent for later launches
-                unsigned int* const counter = p.counters + static_cast<size_t>(n_idx) * gridDim.y + tile_row;
-                if (atomicAdd(counter, 1u) == static_cast<unsigned int>(G - 1))
-                    *counter = 0u;
-            }
-        }
         return;
     }
 
@@ -461,42 +454,11 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                     red[(c0 + i) * kTileM + row_in_tile] = __uint_as_float(r[i]);
             }
         }
-        if (p.counters != nullptr)
-            __threadfence();  // this thread's partial sums are visible device-wide before the CTA is counted below
     }
 
     // ================================================================ cluster reduction and tear-down
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (p.counters != nullptr) {
-        // Workspace parts without a second kernel: the CTAs of one output tile count themselves; whoever arrives last
-        // adds up all the partial tiles (in part order, as splitk_reduce_f32_kernel does, so the result is the same
-        // bit for bit), rounds once and stores C.  The counter goes back to zero for the next launch that uses it.
-        // Only launched with cluster_k == 1.  Nobody waits for anybody.
-        if (threadIdx.x == 0) {
-            unsigned int* const counter = p.counters + static_cast<size_t>(n_idx) * gridDim.y + tile_row;
-            const unsigned int  before  = atomicAdd(counter, 1u);
-            const bool          last    = before == static_cast<unsigned int>(G - 1);
-            if (last)
-                *counter = 0u;
-            *last_flag = last ? 1u : 0u;
-        }
-        __syncthreads();
-        if (*last_flag != 0u && warp >= first_sw) {
-            __threadfence();
-            const int    tid_s    = threadIdx.x - first_sw * 32;
-            const int    n_valid  = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
-            const size_t tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
-            const size_t plane    = static_cast<size_t>(p.M) * p.N;
-            for (int e = tid_s; e < n_valid * kTileM; e += NTS) {
-                const size_t at  = tile_off + static_cast<size_t>(e / kTileM) * p.M + (e % kTileM);
-                float        acc = 0.0f;
-                for (int q = 0; q < G; ++q)
-                    acc += __ldcg(p.partial + q * plane + at);
-                p.out[at] = __float2half_rn(acc);
-            }
-        }
-    }
     if (S > 1) {
         __syncwarp();
         ptx::cluster_sync_all();  // every CTA's partial tile is parked in its shared memory

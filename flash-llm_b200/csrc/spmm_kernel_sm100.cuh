@@ -36,8 +36,6 @@ struct SpmmParams {
     half*         out;           // C (used when workspace_k == 1)
     float*        partial;       // workspace_k fp32 partial matrices [N][M] (used when workspace_k > 1)
     unsigned int* status;        // per-device status word
-    unsigned int* counters;      // one zeroed counter per output tile when the last CTA of a tile sums the workspace
-                                 // parts itself (register-streaming form, cluster_k == 1), else nullptr
     int           M, N, K;
     int           k_tiles;  // K / 64
     SpmmPlan      plan;

@@ -40,20 +40,14 @@ enum PlanField {
     kPlanScatterWarps,    // warps that decompress tiles, one whole tile per warp at a time (4..12, <= a_stages)
     kPlanProducers,       // warps issuing the bulk copies
     kPlanPath,            // how compressed words reach the scatter warps: kPathRing or kPathDirect
-    kPlanReduction,       // who sums workspace parts: kReduceSecondKernel or kReduceLastCta
     kPlanFieldCount
 };
 
 constexpr int kPathRing   = 1;  // bulk copies into a shared-memory ring (spmm_tcgen05_kernel)
 constexpr int kPathDirect = 2;  // global loads into the scatter warps' registers (spmm_tcgen05_direct_kernel)
 
-constexpr int kReduceSecondKernel = 1;  // splitk_reduce_f32_kernel after the SpMM kernel
-constexpr int kReduceLastCta      = 2;  // the last CTA to finish an output tile sums its parts (register-streaming
-                                        // form without clusters; falls back to the second kernel elsewhere)
-
 struct SpmmPlan {
-    int path;       // kPathRing or kPathDirect
-    int reduction;  // kReduceSecondKernel or kReduceLastCta (meaningful when workspace_k > 1)
+    int path;    // kPathRing or kPathDirect
     int n_tile;  // MMA N: 16, 32, 64 or 128
     int cluster_k;
     int workspace_k;

@@ -87,7 +87,7 @@ def reference_chain(shape: ChainShape, x: torch.Tensor, w_qkv: torch.Tensor, w_o
 class DeviceChain:
     """One rank's shards encoded on its GPU plus the buffers of the chain; `step()` enqueues one pass."""
 
-    def __init__(self, fl, shape: ChainShape, shards: dict, device, split_k: int = 8):
+    def __init__(self, fl, shape: ChainShape, shards: dict, device, split_k: int = 64):
         self.fl, self.shape, self.dev, self.split_k = fl, shape, device, split_k
         self.layers = {}
         stream = torch.cuda.current_stream(device).cuda_stream

@@ -145,7 +145,7 @@ void FlashLLM_SetLaunchOverlap(int enable);
 
 /* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
  * csrc/SpMM_API.cu:79-118): fixes launch-plan fields for subsequent calls from this process.  `fields` holds up to
- * eleven ints, 0 = choose automatically, in this order:
+ * ten ints, 0 = choose automatically, in this order:
  *   0 cluster_k       K parts summed inside a thread-block cluster through distributed shared memory (1..8)
  *   1 workspace_k     extra K parts through Reduction_Workspace (capped at Split_K/2 of the call: an fp32 partial
  *                     matrix takes the room of two fp16 ones)
@@ -158,14 +158,10 @@ void FlashLLM_SetLaunchOverlap(int enable);
  *   9 path            1 = ring form: the compressed stream is copied into a shared-memory ring by bulk copies;
  *                     2 = register-streaming form (the default): scatter warps load their tiles' words from global
  *                     memory into registers, tiles alternate between two MMA-issuing threads
- *  10 reduction       who sums the workspace parts: 1 = a second kernel (reference csrc/Reduction_Kernel.cuh; default),
- *                     2 = the last CTA to finish each output tile, for callers that want one launch per call (applies
- *                     to the register-streaming form without clusters and at most 8192 output tiles; measured 5-20 %
- *                     slower on the benchmark shapes); both give the same bits
  * FlashLLM_SetPlan(nullptr, 0) restores automatic choice. */
 void FlashLLM_SetPlan(const int* fields, int count);
 
-/* Describes the plan the next SpMM call with these sizes would use: out[0..10] as above, out[11] = dynamic shared
+/* Describes the plan the next SpMM call with these sizes would use: out[0..9] as above, out[10] = dynamic shared
  * memory in bytes; `count` = entries available in `out`. */
 int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count);
 

@@ -118,47 +118,3 @@ def test_malformed_offsets_are_reported_not_followed(lib, form):
         DeviceProblem(lib, comp, offs, B, M, N, K, 1).run()
     finally:
         lib.set_plan()
-
-
-@pytest.mark.parametrize("M,K,N,split_k,workspace_k", [(256, 2048, 16, 8, 4), (1024, 4096, 32, 6, 3), (512, 8192, 8, 4, 2),
-                                                      (384, 1024, 64, 16, 8), (2048, 2048, 128, 4, 2)])
-def test_last_cta_reduction_gives_the_bits_of_the_second_kernel(lib, oracle, M, K, N, split_k, workspace_k):
-    """Workspace parts summed by the last CTA of each output tile or by the reduction kernel: same order, same bits;
-    run twice in a row so that the self-resetting arrival counters are used again."""
-    A, B = random_problem(lib, M, K, N, 0.8, 77 + N)
-    comp, offs, _ = lib.InitSparseMatrixA_API(A)
-    prob = DeviceProblem(lib, comp, offs, B, M, N, K, split_k)
-    results = {}
-    for reduction in (1, 2, 2):
-        lib.set_plan(path=2, cluster_k=1, workspace_k=workspace_k, reduction=reduction)
-        try:
-            assert lib.get_plan(M, N, K, split_k)["reduction"] == reduction
-            results.setdefault(reduction, []).append(prob.run().copy())
-        finally:
-            lib.set_plan()
-    assert_close(results[1][0], oracle.gemm_f32(A, B), "second-kernel reduction")
-    for got in results[2]:
-        assert np.array_equal(got.view(np.uint16), results[1][0].view(np.uint16))
-
-
-def test_last_cta_reduction_on_many_streams(lib, oracle):
-    """Calls in flight at the same time on different streams take different counter regions."""
-    M, K, N, split_k = 1024, 4096, 16, 8
-    A, B = random_problem(lib, M, K, N, 0.8, 91)
-    comp, offs, _ = lib.InitSparseMatrixA_API(A)
-    want = oracle.gemm_f32(A, B)
-    probs = [DeviceProblem(lib, comp, offs, B, M, N, K, split_k) for _ in range(6)]
-    streams = [torch.cuda.Stream() for _ in probs]
-    lib.set_plan(path=2, cluster_k=1, workspace_k=4, reduction=2)
-    try:
-        for _ in range(5):
-            for prob, s in zip(probs, streams):
-                with torch.cuda.stream(s):
-                    lib.SpMM_SplitK_API(s.cuda_stream, None, prob.comp.data_ptr(), prob.offs.data_ptr(), prob.B.data_ptr(),
-                                        prob.C.data_ptr(), M, N, K, prob.ws.data_ptr(), split_k)
-        torch.cuda.synchronize()
-    finally:
-        lib.set_plan()
-    assert lib.consume_status() == 0
-    for prob in probs:
-        assert_close(prob.C.cpu().numpy(), want, "concurrent streams")
