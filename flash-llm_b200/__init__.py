@@ -5,6 +5,8 @@ side: it loads the library through its C ABI and mirrors the reference's operato
 fallback: if the library is missing or cannot be loaded, importing :mod:`api` members raises.
 """
 from .api import (  # noqa: F401
+    ACT_NONE,
+    ACT_RELU,
     LIBRARY_PATH,
     FlashLLMError,
     GenSparseMatrixBinFile,
@@ -20,6 +22,7 @@ from .api import (  # noqa: F401
     set_launch_overlap,
     set_plan,
     splitk_reduction,
+    spmm_splitk_bias_act,
     spmm_splitk_no_alloc,
 )
 from . import synthetic  # noqa: F401

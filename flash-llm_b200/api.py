@@ -47,6 +47,8 @@ def library() -> C.CDLL:
     L = C.CDLL(LIBRARY_PATH)
     L.FlashLLM_SpMM_SplitK.restype = C.c_int
     L.FlashLLM_SpMM_SplitK.argtypes = [C.c_void_p] * 3 + [C.c_void_p] * 3 + [C.c_int] * 3 + [C.c_void_p, C.c_int]
+    L.FlashLLM_SpMM_SplitK_BiasAct.restype = C.c_int
+    L.FlashLLM_SpMM_SplitK_BiasAct.argtypes = ([C.c_void_p] * 5 + [C.c_int] * 3 + [C.c_void_p, C.c_int, C.c_void_p, C.c_int])
     for name in ("FlashLLM_InitSparseMatrixA", "FlashLLM_InitSparseMatrixA_NoReorder"):
         f = getattr(L, name)
         f.restype = C.c_int
@@ -134,6 +136,19 @@ def SpMM_SplitK_API(stream: int, A: int | None, Compressed_A: int, TileOffsets: 
     code = library().FlashLLM_SpMM_SplitK(stream, A, Compressed_A, TileOffsets, B, C_out, M, N, K,
                                           Reduction_Workspace, Split_K)
     _check(code, f"SpMM_SplitK_API(M={M}, N={N}, K={K}, Split_K={Split_K})")
+
+
+ACT_NONE, ACT_RELU = 0, 1
+
+
+def spmm_splitk_bias_act(stream: int, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int, N: int, K: int,
+                         Reduction_Workspace: int | None, Split_K: int, bias: int | None = None,
+                         activation: int = ACT_NONE) -> None:
+    """``C[N][M] = act(B[N][K] @ A[M][K]^T + bias[M])`` with the epilogue applied to the fp32 sums before the one fp16
+    rounding; ``bias`` is a device pointer to M halves or ``None``, ``activation`` ``ACT_NONE`` or ``ACT_RELU``."""
+    code = library().FlashLLM_SpMM_SplitK_BiasAct(stream, Compressed_A, TileOffsets, B, C_out, M, N, K,
+                                                  Reduction_Workspace, Split_K, bias, activation)
+    _check(code, f"SpMM_SplitK_BiasAct(M={M}, N={N}, K={K}, Split_K={Split_K})")
 
 
 def spmm_splitk_no_alloc(stream: int, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int, N: int, K: int,

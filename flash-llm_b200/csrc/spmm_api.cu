@@ -319,7 +319,8 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
 }
 
-static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws, long long count, int parts)
+static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws, long long count, int parts,
+                                   const half* bias, int M, int activation)
 {
     const int       threads = 256;
     const long long groups  = (count + 3) / 4;
@@ -336,7 +337,7 @@ static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws
         cfg.attrs                                          = attr;
         cfg.numAttrs                                       = 1;
     }
-    return cudaLaunchKernelEx(&cfg, splitk_reduce_f32_kernel, C, ws, count, parts);
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_f32_kernel, C, ws, count, parts, bias, M, activation);
 }
 
 static cudaError_t reduce_workspace(cudaStream_t stream, half* C, const half* ws, long long count, int parts)
@@ -359,19 +360,20 @@ static bool n_supported(int N)
 
 using namespace flashllm;
 
-cudaError_t SpMM_SplitK_API(cudaStream_t stream,
-                            const half*  A,
-                            const uint4* Compressed_A,
-                            const int*   TileOffsets,
-                            const half*  B,
-                            half*        C,
-                            const int    M_Global,
-                            const int    N_Global,
-                            const int    K_Global,
-                            half*        Reduction_Workspace,
-                            int          Split_K)
+// SpMM_SplitK_API plus the output epilogue (bias of output feature m, activation) the public entry points select.
+static cudaError_t spmm_launch_all(cudaStream_t stream,
+                                   const uint4* Compressed_A,
+                                   const int*   TileOffsets,
+                                   const half*  B,
+                                   half*        C,
+                                   const int    M_Global,
+                                   const int    N_Global,
+                                   const int    K_Global,
+                                   half*        Reduction_Workspace,
+                                   int          Split_K,
+                                   const half*  bias,
+                                   int          activation)
 {
-    (void)A;  // kept for signature compatibility; callers pass nullptr
     if (!n_supported(N_Global)) {
         printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
         return cudaErrorUnknown;
@@ -403,6 +405,8 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     params.out          = C;
     params.partial      = pl.workspace_k > 1 ? reinterpret_cast<float*>(Reduction_Workspace) : nullptr;
     params.status       = st->status;
+    params.bias         = bias;
+    params.activation   = activation;
     params.M            = M_Global;
     params.N            = N_Global;
     params.K            = K_Global;
@@ -434,11 +438,50 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
     if (err != cudaSuccess)
         return err;
     if (pl.workspace_k > 1)
-        return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k);
+        return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k,
+                               bias, M_Global, activation);
     return cudaSuccess;
 }
 
+cudaError_t SpMM_SplitK_API(cudaStream_t stream,
+                            const half*  A,
+                            const uint4* Compressed_A,
+                            const int*   TileOffsets,
+                            const half*  B,
+                            half*        C,
+                            const int    M_Global,
+                            const int    N_Global,
+                            const int    K_Global,
+                            half*        Reduction_Workspace,
+                            int          Split_K)
+{
+    (void)A;  // kept for signature compatibility; callers pass nullptr
+    return spmm_launch_all(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global, Reduction_Workspace,
+                           Split_K, nullptr, kActNone);
+}
+
 extern "C" {
+
+int FlashLLM_SpMM_SplitK_BiasAct(void*       stream,
+                                 const void* Compressed_A,
+                                 const int*  TileOffsets,
+                                 const void* B,
+                                 void*       C,
+                                 int         M,
+                                 int         N,
+                                 int         K,
+                                 void*       Reduction_Workspace,
+                                 int         Split_K,
+                                 const void* bias,
+                                 int         activation)
+{
+    if (activation != kActNone && activation != kActRelu)
+        return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(spmm_launch_all(static_cast<cudaStream_t>(stream), static_cast<const uint4*>(Compressed_A),
+                                            TileOffsets, static_cast<const half*>(B), static_cast<half*>(C), M, N, K,
+                                            static_cast<half*>(Reduction_Workspace), Split_K,
+                                            static_cast<const half*>(bias), activation));
+}
 
 int FlashLLM_SpMM_SplitK(void*       stream,
                          const void* A,

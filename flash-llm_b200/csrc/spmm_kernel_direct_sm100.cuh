@@ -444,7 +444,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                             if (part_tile)
                                 part_tile[at] = __uint_as_float(r[i]);
                             else
-                                out_tile[at] = __float2half_rn(__uint_as_float(r[i]));
+                                out_tile[at] = finish_output(__uint_as_float(r[i]), p.bias,
+                                                             tile_row * kTileM + row_in_tile, p.activation);
                         }
                 }
             }
@@ -483,7 +484,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                     if (part_tile)
                         part_tile[static_cast<size_t>(n) * p.M + m] = acc;
                     else
-                        out_tile[static_cast<size_t>(n) * p.M + m] = __float2half_rn(acc);
+                        out_tile[static_cast<size_t>(n) * p.M + m] =
+                            finish_output(acc, p.bias, tile_row * kTileM + m, p.activation);
                 }
             }
         }

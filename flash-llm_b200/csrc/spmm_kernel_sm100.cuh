@@ -36,12 +36,28 @@ struct SpmmParams {
     half*         out;           // C (used when workspace_k == 1)
     float*        partial;       // workspace_k fp32 partial matrices [N][M] (used when workspace_k > 1)
     unsigned int* status;        // per-device status word
+    const half*   bias;          // [M] added to every output row before the activation, or nullptr
+    int           activation;    // kActNone or kActRelu, applied to the fp32 sum before the one fp16 rounding
     int           M, N, K;
     int           k_tiles;  // K / 64
     SpmmPlan      plan;
 };
 
 constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
+
+// Output epilogue shared by every place that rounds a finished fp32 sum to fp16: optional bias of output feature m,
+// optional ReLU.  (The reference's callers do this in a separate pass over fp16 C, third_party/ft.patch
+// ParallelGpt FFN: add_bias_relu after the first FFN GEMM; here it costs one add and one max before the rounding.)
+constexpr int kActNone = 0, kActRelu = 1;
+
+__device__ __forceinline__ half finish_output(float acc, const half* bias, int m, int activation)
+{
+    if (bias != nullptr)
+        acc += __half2float(bias[m]);
+    if (activation == kActRelu)
+        acc = fmaxf(acc, 0.0f);
+    return __float2half_rn(acc);
+}
 
 // Pipeline-analysis builds (never the shipped one) drop one stage of the kernel to see what it costs, as the
 // reference does with its own stubs (csrc/SpMM_Kernel.cuh:64-111).  Bits: 1 no zero-fill, 2 no scatter stores,
@@ -692,7 +708,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                             if (part_tile)
                                 part_tile[at] = __uint_as_float(r[i]);
                             else
-                                out_tile[at] = __float2half_rn(__uint_as_float(r[i]));
+                                out_tile[at] = finish_output(__uint_as_float(r[i]), p.bias,
+                                                             tile_row * kTileM + row_in_tile, p.activation);
                         }
                 }
             }
@@ -731,7 +748,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
                     if (part_tile)
                         part_tile[static_cast<size_t>(n) * p.M + m] = acc;
                     else
-                        out_tile[static_cast<size_t>(n) * p.M + m] = __float2half_rn(acc);
+                        out_tile[static_cast<size_t>(n) * p.M + m] =
+                            finish_output(acc, p.bias, tile_row * kTileM + m, p.activation);
                 }
             }
         }
@@ -751,7 +769,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 
 // Sums the fp32 partial matrices this library parks in the caller's workspace when workspace_k > 1 and rounds once:
 // C[i] = fp16(sum_s ws[s*count + i]); four outputs per thread.
-__global__ void splitk_reduce_f32_kernel(half* __restrict__ C, const float* __restrict__ ws, long long count, int parts)
+__global__ void splitk_reduce_f32_kernel(half* __restrict__ C, const float* __restrict__ ws, long long count, int parts,
+                                         const half* __restrict__ bias, int M, int activation)
 {
     ptx::grid_launch_dependents();  // the next SpMM may begin streaming its weights
     ptx::grid_dependency_wait();    // the partial matrices come from the SpMM launched just before
@@ -766,10 +785,13 @@ __global__ void splitk_reduce_f32_kernel(half* __restrict__ C, const float* __re
         acc.z += v.z;
         acc.w += v.w;
     }
-    uint2    o;
-    __half2* oh = reinterpret_cast<__half2*>(&o);
-    oh[0]       = __floats2half2_rn(acc.x, acc.y);
-    oh[1]       = __floats2half2_rn(acc.z, acc.w);
+    const int m = static_cast<int>(i4 % M);  // C is [N][M] and M is a multiple of 4: the four share a row of C
+    uint2     o;
+    half*     oh = reinterpret_cast<half*>(&o);
+    oh[0]        = finish_output(acc.x, bias, m, activation);
+    oh[1]        = finish_output(acc.y, bias, m + 1, activation);
+    oh[2]        = finish_output(acc.z, bias, m + 2, activation);
+    oh[3]        = finish_output(acc.w, bias, m + 3, activation);
     *reinterpret_cast<uint2*>(C + i4) = o;
 }
 

@@ -61,15 +61,16 @@ def shard_weights(shape: ChainShape, rank: int, w_qkv: torch.Tensor, w_out: torc
             "ffn2": w_ffn2[:, rank * f:(rank + 1) * f].contiguous()}
 
 
-def run_chain(shape: ChainShape, x: torch.Tensor, matmul: Callable[[str, torch.Tensor], torch.Tensor],
+def run_chain(shape: ChainShape, x: torch.Tensor, matmul: Callable[..., torch.Tensor],
               all_reduce: Callable[[torch.Tensor], torch.Tensor]) -> torch.Tensor:
-    """One rank's pass over the layer.  `matmul(name, X[N][K]) -> Y[N][M]` multiplies by that rank's shard `name`;
+    """One rank's pass over the layer.  `matmul(name, X[N][K], relu=False) -> Y[N][M]` multiplies by that rank's shard
+    `name` (and applies ReLU to the result when asked: FFN1 is column-parallel, so its activation needs no partner);
     `all_reduce(t)` returns the sum of `t` over the ranks.  Returns the layer output [N][H] (same on every rank)."""
     h = shape.hidden // shape.world
     y_qkv = matmul("qkv", x)                               # [N][3H/g]: this rank's Q, K, V features
     v = y_qkv[:, 2 * h:3 * h].contiguous()                 # single-position attention returns V
     attn = all_reduce(matmul("out_proj", v))               # [N][H], partial sums over the K slices
-    y1 = torch.relu(matmul("ffn1", attn))                  # [N][F/g]
+    y1 = matmul("ffn1", attn, relu=True)                   # [N][F/g]
     return all_reduce(matmul("ffn2", y1))                  # [N][H]
 
 
@@ -107,13 +108,14 @@ class DeviceChain:
         self.ws = torch.empty((split_k, N, biggest), dtype=torch.float16, device=device)
         torch.cuda.synchronize(device)
 
-    def matmul(self, name: str, x: torch.Tensor) -> torch.Tensor:
+    def matmul(self, name: str, x: torch.Tensor, relu: bool = False) -> torch.Tensor:
         layer = self.layers[name]
         assert x.is_contiguous() and x.dtype == torch.float16 and tuple(x.shape) == (self.shape.tokens, layer["K"])
         stream = torch.cuda.current_stream(self.dev).cuda_stream
-        self.fl.SpMM_SplitK_API(stream, None, layer["comp"].data_ptr(), layer["offs"].data_ptr(), x.data_ptr(),
-                                layer["out"].data_ptr(), layer["M"], self.shape.tokens, layer["K"], self.ws.data_ptr(),
-                                self.split_k)
+        self.fl.spmm_splitk_bias_act(stream, layer["comp"].data_ptr(), layer["offs"].data_ptr(), x.data_ptr(),
+                                     layer["out"].data_ptr(), layer["M"], self.shape.tokens, layer["K"],
+                                     self.ws.data_ptr(), self.split_k, None,
+                                     self.fl.ACT_RELU if relu else self.fl.ACT_NONE)
         return layer["out"]
 
     def step(self, x: torch.Tensor, all_reduce: Callable[[torch.Tensor], torch.Tensor]) -> torch.Tensor:

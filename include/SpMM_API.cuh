@@ -105,6 +105,24 @@ int FlashLLM_EncodeOnDevice_TileOffsets(void* stream, const void* A_d, int M, in
 int FlashLLM_EncodeOnDevice_Pack(void* stream, const void* A_d, int M, int K, const int* TileOffsets_d,
                                  uint32_t* Compressed_A_d, int reorder);
 
+/* SpMM with the output epilogue of the reference's feed-forward call sites fused in (no counterpart in the reference
+ * library: FasterTransformer runs add-bias + ReLU as a separate pass over C after the first FFN GEMM,
+ * third_party/ft.patch ParallelGpt FFN layer): C[n][m] = act(sum_k A[m][k] * B[n][k] + bias[m]), computed on the fp32
+ * sum and rounded to fp16 once.  `bias` is a device pointer to M halves or nullptr; `activation` 0 = none, 1 = ReLU.
+ * Other arguments and results as FlashLLM_SpMM_SplitK (without the unused `A`). */
+int FlashLLM_SpMM_SplitK_BiasAct(void*       stream,
+                                 const void* Compressed_A,
+                                 const int*  TileOffsets,
+                                 const void* B,
+                                 void*       C,
+                                 int         M,
+                                 int         N,
+                                 int         K,
+                                 void*       Reduction_Workspace,
+                                 int         Split_K,
+                                 const void* bias,
+                                 int         activation);
+
 /* SpMM for callers that must not allocate device memory.  (No counterpart in the reference, whose callers always
  * bring a Reduction_Workspace of their own.)  Some hosts of this library cannot call cudaMalloc at the point where
  * they need the product: code running while a CUDA graph is being captured, a serving loop whose memory pool was

@@ -49,10 +49,10 @@ def _worker(rank: int, world: int, port: int, H: int, F: int, N: int, failures):
             encoded[name] = (comp, offs, w.shape[0], w.shape[1])
         x = fl.synthetic.normal_matrix(N, H, 1.0, 901).to(torch.float16)
 
-        def matmul(name, act):
+        def matmul(name, act, relu=False):
             comp, offs, M, K = encoded[name]
-            out = cpu_oracle.spmm_splitk(comp, offs, act.contiguous().numpy(), M, N, K, 1)
-            return torch.from_numpy(out.copy())
+            out = torch.from_numpy(cpu_oracle.spmm_splitk(comp, offs, act.contiguous().numpy(), M, N, K, 1).copy())
+            return torch.relu(out) if relu else out
 
         def all_reduce(t):
             acc = t.float()

@@ -32,7 +32,7 @@ def test_chain_on_one_device_matches_the_host_layer(lib, oracle, H, F, world):
 
     v = [c.matmul("qkv", x_d)[:, 2 * h:3 * h].contiguous() for c in chains]
     attn = summed("out_proj", v)
-    y1 = [torch.relu(c.matmul("ffn1", attn)).clone() for c in chains]
+    y1 = [c.matmul("ffn1", attn, relu=True).clone() for c in chains]
     got = summed("ffn2", y1)
     torch.cuda.synchronize()
     assert lib.consume_status() == 0
