@@ -51,6 +51,13 @@ __device__ __forceinline__ void scatter_vector_aligned(uint32_t stage, const uin
     scatter_word_aligned(stage, w.w);
 }
 
+// How many of its own tiles ahead a scatter warp asks the memory system to bring into L2 (its register loads run one
+// tile ahead).
+#ifndef FLASHLLM_PREFETCH_AHEAD
+#define FLASHLLM_PREFETCH_AHEAD 2
+#endif
+constexpr int kPrefetchAhead = FLASHLLM_PREFETCH_AHEAD;
+
 // Warps of the register-streaming kernel: one B loader, kDirectIssuers MMA issuers, then the scatter warps.
 constexpr int kDirectIssuers = 2;
 
@@ -303,9 +310,13 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                     if (q * 32 + lane < n_in)
                         nxt[q] = ldg_stream16(src + q * 32 + lane);
                 }
-                if (lane == 0 && sw + NSW < L && offs[sw + NSW + 1] > offs[sw + NSW])
-                    ptx::prefetch_l2_bulk(p.compressed + offs[sw + NSW],
-                                          static_cast<uint32_t>(offs[sw + NSW + 1] - offs[sw + NSW]) * 16u);
+                if (lane == 0) {
+                    for (int a = 1; a < kPrefetchAhead; ++a) {
+                        const int t = sw + a * NSW;
+                        if (t < L && offs[t + 1] > offs[t])
+                            ptx::prefetch_l2_bulk(p.compressed + offs[t], static_cast<uint32_t>(offs[t + 1] - offs[t]) * 16u);
+                    }
+                }
             }
             uint32_t use = 0;
             for (int j = sw; j < L; j += NSW, ++use) {
@@ -392,8 +403,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                     }
                     // ... and pull the one after it from DRAM into L2, so that its register loads, issued one tile
                     // from now, only have the L2 latency left to hide
-                    if (lane == 0 && j + 2 * NSW < L) {
-                        const int pb = offs[j + 2 * NSW], pe = offs[j + 2 * NSW + 1];
+                    if (lane == 0 && j + kPrefetchAhead * NSW < L) {
+                        const int pb = offs[j + kPrefetchAhead * NSW], pe = offs[j + kPrefetchAhead * NSW + 1];
                         if (pe > pb)
                             ptx::prefetch_l2_bulk(p.compressed + pb, static_cast<uint32_t>(pe - pb) * 16u);
                     }
