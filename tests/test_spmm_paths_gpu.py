@@ -118,3 +118,11 @@ def test_malformed_offsets_are_reported_not_followed(lib, form):
         DeviceProblem(lib, comp, offs, B, M, N, K, 1).run()
     finally:
         lib.set_plan()
+
+
+@pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
+@pytest.mark.parametrize("N", [256, 384])
+def test_n_beyond_one_mma_tile(lib, oracle, form, N):
+    """N a multiple of 128 (the reference's large-N dispatch, csrc/SpMM_API.cu:97-112): several N tiles per tile row."""
+    A, B = random_problem(lib, 256, 1024, N, 0.8, 500 + N)
+    _check(lib, oracle, A, B, N, 4, dict(**form), f"N={N}")
