@@ -226,14 +226,16 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // tables (kernel_benchmark/benchmark.sh:13-15).
     const int slots     = st->sm_count * (two_per_sm ? 2 : 1);
     const int max_extra = ((static_cast<long long>(M) * N) % 4 != 0) ? 1 : (Split_K / 2 > 1 ? Split_K / 2 : 1);
-    const bool small    = static_cast<long long>(tile_rows) * k_tiles <= 4096;
+    // (with launch overlap on, the second kernel hides behind its neighbours and workspace parts win at every size)
+    const bool small    = static_cast<long long>(tile_rows) * k_tiles <= 4096
+                       && g_launch_overlap.load(std::memory_order_relaxed) == 0;
     int        best_s = 1, best_g = 1;
     if (!small) {
         double best_cost = 0.0;
         for (int g = 1; g <= max_extra && g <= 32 && g <= k_tiles; ++g) {
             const long long ctas  = static_cast<long long>(ctas_flat) * g;
             const double    waves = static_cast<double>((ctas + slots - 1) / slots);
-            const double    cost  = waves * (static_cast<double>(k_tiles) / g + 16.0) + (g > 1 ? 0.5 * g : 0.0);
+            const double    cost  = waves * (static_cast<double>((k_tiles + g - 1) / g) + 16.0) + (g > 1 ? 0.5 * g : 0.0);
             if (g == 1 || cost < best_cost) {
                 best_cost = cost;
                 best_g    = g;
