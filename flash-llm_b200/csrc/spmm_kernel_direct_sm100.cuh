@@ -165,11 +165,7 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     }
     // Offsets that run backwards, or tiles above 2048 vectors, would make the roles below disagree about who owns
     // which vectors; the whole slice is checked before any of them starts.
-    bool bad_slice = false;
-    for (int i = threadIdx.x; i < L; i += blockDim.x) {
-        const int lo = offs_global[i], hi = offs_global[i + 1];
-        bad_slice |= (lo < 0) || (hi < lo) || (hi - lo > kMaxTileVectors);
-    }
+    bool bad_slice = offsets_slice_is_bad(offs_global, L);
     ptx::tc_fence_before_sync();
     bad_slice = __syncthreads_or(bad_slice ? 1 : 0) != 0;
     ptx::tc_fence_after_sync();
@@ -187,33 +183,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     if (warp == b_warp) {
         // ================================================================ B loader: KB K tiles per TMA instruction
         if (lane == 0 && L > 0 && go) {
-            ptx::grid_dependency_wait();
-            const int batches = (L + KB - 1) / KB;
-            int       bs      = 0;
-            uint32_t  use     = 0;
-            int       issued  = 0;
-            for (int b = 0; b < batches; ++b) {
-                if (!wait_bounded_relaxed(b_empty + 8u * bs, (use & 1u) ^ 1u, abort_flag, p.status))
-                    break;
-                const uint32_t bar = b_full + 8u * bs;
-                ptx::mbar_arrive_expect_tx(bar, KB * kBSlab);
-                ptx::tma_load_3d(b_base + bs * KB * kBSlab, &tmap_b, 0, n_idx * N_TILE, k_begin + b * KB, bar);
-                ++issued;
-                if (++bs == b_stages) {
-                    bs = 0;
-                    ++use;
-                }
-            }
-            if (*abort_flag) {
-                // Give copies already issued a bounded chance to land before the CTA may exit.
-                const uint64_t t_leave = ptx::globaltimer_ns();
-                for (int back = 1; back <= b_stages && back <= issued; ++back) {
-                    const int      bb  = issued - back;
-                    const uint32_t bar = b_full + 8u * (bb % b_stages);
-                    while (!ptx::mbar_test_wait(bar, (bb / b_stages) & 1u)
-                           && ptx::globaltimer_ns() - t_leave < 2000000ull) {}
-                }
-            }
+            load_b_batches(&tmap_b, (L + KB - 1) / KB, KB, b_stages, kBSlab, b_base, b_full, b_empty, n_idx * N_TILE, k_begin,
+                           abort_flag, p.status);
         }
     }
     else if (warp < first_sw) {
@@ -421,51 +392,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
         acc_ok = __all_sync(0xFFFFFFFFu, acc_ok && (*abort_flag == 0u));
         ptx::tc_fence_after_sync();
 
-        const int quarter     = warp & 3;  // TMEM lanes this warp may read: 32*quarter ..
-        constexpr int per_quarter = NSW >= 8 ? 2 : 1;  // warps sharing a lane quarter split the columns
-        const int col_share   = (N_TILE / per_quarter) < 8 ? 8 : (N_TILE / per_quarter);
-        const int col_begin   = sw < 4 * per_quarter ? (sw / 4) * col_share : N_TILE;  // the remaining warps idle
-        const int col_end     = (col_begin + col_share) < N_TILE ? (col_begin + col_share) : N_TILE;
-        const int n_valid     = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
-        const int row_in_tile = quarter * 32 + lane;
-        const size_t tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
-        half* const  out_tile  = p.out + tile_off;
-        float* const part_tile = G > 1 ? p.partial + static_cast<size_t>(g) * p.M * p.N + tile_off : nullptr;
-        float* const red       = reinterpret_cast<float*>(smem);  // [N_TILE][128] fp32, over the idle A stages
-
-        for (int c0 = col_begin; c0 < col_end; c0 += 8) {
-            uint32_t r[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                r[i] = 0u;
-            for (int m = 0; m < MI && m < L; ++m) {  // an issuer without tiles never wrote its accumulator
-                uint32_t t[8];
-                ptx::tmem_ld_x8(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + m * N_TILE + c0, t);
-                ptx::tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(t[i]));
-            }
-            if (S == 1) {
-                if (acc_ok) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        if (c0 + i < n_valid) {
-                            const size_t at = static_cast<size_t>(c0 + i) * p.M + row_in_tile;
-                            if (part_tile)
-                                part_tile[at] = __uint_as_float(r[i]);
-                            else
-                                out_tile[at] = finish_output(__uint_as_float(r[i]), p.bias,
-                                                             tile_row * kTileM + row_in_tile, p.activation);
-                        }
-                }
-            }
-            else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    red[(c0 + i) * kTileM + row_in_tile] = __uint_as_float(r[i]);
-            }
-        }
+        accumulators_to_output<N_TILE>(p, tmem_acc, L < MI ? L : MI, N_TILE, warp & 3, lane, sw, NSW >= 8 ? 2 : 1, S, G, g,
+                                       n_idx, tile_row, acc_ok, reinterpret_cast<float*>(smem));
     }
 
     // ================================================================ cluster reduction and tear-down
@@ -474,32 +402,9 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     if (S > 1) {
         __syncwarp();
         ptx::cluster_sync_all();  // every CTA's partial tile is parked in its shared memory
-        if (warp >= first_sw) {
-            const int    tid_s    = threadIdx.x - first_sw * 32;
-            const int    n_valid  = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
-            const int    total    = N_TILE * kTileM;
-            const int    lo       = static_cast<int>(static_cast<long long>(total) * rank / S);
-            const int    hi       = static_cast<int>(static_cast<long long>(total) * (rank + 1) / S);
-            const bool   store_ok = (*abort_flag == 0u);
-            const size_t tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
-            half* const  out_tile  = p.out + tile_off;
-            float* const part_tile = G > 1 ? p.partial + static_cast<size_t>(g) * p.M * p.N + tile_off : nullptr;
-            for (int e = lo + tid_s; e < hi; e += NTS) {
-                const int n = e / kTileM, m = e % kTileM;
-                if (n >= n_valid)
-                    break;
-                float acc = 0.0f;
-                for (int q = 0; q < S; ++q)
-                    acc += ptx::ld_dsmem_f32(ptx::map_to_rank(base + static_cast<uint32_t>(e) * 4u, q));
-                if (store_ok) {
-                    if (part_tile)
-                        part_tile[static_cast<size_t>(n) * p.M + m] = acc;
-                    else
-                        out_tile[static_cast<size_t>(n) * p.M + m] =
-                            finish_output(acc, p.bias, tile_row * kTileM + m, p.activation);
-                }
-            }
-        }
+        if (warp >= first_sw)
+            cluster_reduce_store<N_TILE>(p, base, rank, S, G, g, n_idx, tile_row, threadIdx.x - first_sw * 32, NTS,
+                                         *abort_flag == 0u);
         __syncwarp();
         ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     }
