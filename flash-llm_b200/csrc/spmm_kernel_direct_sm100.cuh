@@ -8,9 +8,8 @@
 //     the reference's LDG.128 scheme, csrc/SpMM_Kernel.cuh:17-62) right after it has published the current one, so
 //     a whole hand-back period of the stage (several microseconds) hides the memory latency, and as many tiles as
 //     there are scatter warps are in flight per CTA.  No copy ring, no producer warps, no per-chunk barriers.
-//   * The scatter warps are bound by latency chains and by the instructions they issue per tile, not by
-//     shared-memory bandwidth, so a stage is cleared with 32 16-byte stores per lane, which take fewer instructions
-//     than any per-word scheme.  Tiles with more vectors than the register budget (CAP per lane) fetch and scatter
+//   * A stage is cleared with 32 16-byte stores per lane: clearing only the cells the previous tile wrote (their
+//     locations kept in registers) takes more, and slower, store instructions and measured slower.  Tiles with more vectors than the register budget (CAP per lane) fetch and scatter
 //     the excess in a plain loop.
 #pragma once
 #include "spmm_kernel_sm100.cuh"
@@ -27,28 +26,6 @@ __device__ __forceinline__ uint4 ldg_stream16(const uint4* ptr)
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(ptr));
     return v;
-}
-
-// smem[stage + 2*loc] = value for one tiled-CSL word; locations are masked to the 8192 cells of a tile, so a corrupt
-// word cannot leave the stage.
-__device__ __forceinline__ void scatter_word_aligned(uint32_t stage, uint32_t word)
-{
-#if (FLASHLLM_ABLATE & 64)
-    // timing only: a full-word store of the same instruction count (wrong values)
-    asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage + ((word >> 15) & 0x3FFCu)), "r"(word) : "memory");
-#else
-    asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + ((word >> 15) & 0x3FFEu)),
-                 "h"(static_cast<unsigned short>(word & 0xFFFFu))
-                 : "memory");
-#endif
-}
-
-__device__ __forceinline__ void scatter_vector_aligned(uint32_t stage, const uint4& w)
-{
-    scatter_word_aligned(stage, w.x);
-    scatter_word_aligned(stage, w.y);
-    scatter_word_aligned(stage, w.z);
-    scatter_word_aligned(stage, w.w);
 }
 
 // How many of its own tiles ahead a scatter warp asks the memory system to bring into L2 (its register loads run one
@@ -328,9 +305,9 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                     if (q * 32 + lane < n_reg) {
 #if (FLASHLLM_ABLATE & 2)
                         if ((nxt[q].x ^ nxt[q].y ^ nxt[q].z ^ nxt[q].w) == 0x9E3779B9u)  // keeps the loads alive
-                            scatter_word_aligned(stage, nxt[q].x);
+                            scatter_word(stage, nxt[q].x);
 #else
-                        scatter_vector_aligned(stage, nxt[q]);
+                        scatter_vector(stage, nxt[q]);
 #endif
                     }
                 }
@@ -349,7 +326,7 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                         if (v0 + q * 32 >= n_in)
                             break;
                         if (v0 + q * 32 + lane < n_in)
-                            scatter_vector_aligned(stage, nxt[q]);
+                            scatter_vector(stage, nxt[q]);
                     }
                 }
                 if (lane == 0)
