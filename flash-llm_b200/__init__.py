@@ -16,13 +16,19 @@ from .api import (  # noqa: F401
     build_library,
     consume_status,
     encode_on_device,
+    gen_sparse_matrix_bin_file_device,
     get_plan,
     launch_count,
     library,
+    load_sparse_matrix_bin_files,
+    read_output_sizes,
+    read_rank_lists,
+    read_sparse_matrix_bin_files,
     set_launch_overlap,
     set_plan,
     splitk_reduction,
     spmm_splitk_bias_act,
     spmm_splitk_no_alloc,
+    write_rank_lists,
 )
 from . import synthetic  # noqa: F401

@@ -60,6 +60,18 @@ def library() -> C.CDLL:
     L.FlashLLM_EncodeOnDevice_Pack.restype = C.c_int
     L.FlashLLM_EncodeOnDevice_Pack.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                C.c_int]
+    L.FlashLLM_GenSparseMatrixBinFile_Device.restype = C.c_int
+    L.FlashLLM_GenSparseMatrixBinFile_Device.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_char_p, C.c_char_p, C.c_char_p]
+    L.FlashLLM_ReadOutputSizes.restype = C.c_int
+    L.FlashLLM_ReadOutputSizes.argtypes = [C.c_char_p, _i32p, _i32p]
+    L.FlashLLM_ReadSparseMatrixBinFiles.restype = C.c_int
+    L.FlashLLM_ReadSparseMatrixBinFiles.argtypes = [C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    L.FlashLLM_LoadSparseMatrixBinFiles.restype = C.c_int
+    L.FlashLLM_LoadSparseMatrixBinFiles.argtypes = [C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    for name in ("FlashLLM_WriteRankLists", "FlashLLM_ReadRankLists"):
+        f = getattr(L, name)
+        f.restype = C.c_int
+        f.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
     L.FlashLLM_SpMM_SplitK_NoAlloc.restype = C.c_int
     L.FlashLLM_SpMM_SplitK_NoAlloc.argtypes = [C.c_void_p] * 5 + [C.c_int] * 4
     L.FlashLLM_SplitK_Reduction.restype = C.c_int
@@ -125,6 +137,68 @@ def GenSparseMatrixBinFile(dense_file: str, M: int, K: int, nz_weights_file: str
     """File-to-file conversion (reference csrc/SpMM_API.cu:500-555), byte-compatible outputs."""
     library().GenSparseMatrixBinFile(dense_file.encode(), M, K, nz_weights_file.encode(), tile_offsets_file.encode(),
                                      output_sizes_file.encode())
+
+
+_FILE_ERRORS = {-1: "a file cannot be opened or created", -2: "a file is shorter than asked for",
+                -3: "the contents are not a well-formed tiled-CSL matrix", -4: "bad arguments"}
+
+
+def _check_file(code: int, what: str) -> None:
+    if code != 0:
+        raise FlashLLMError(f"{what}: {_FILE_ERRORS.get(code, f'cudaError_t {code}')}")
+
+
+def gen_sparse_matrix_bin_file_device(dense_file: str, M: int, K: int, nz_weights_file: str, tile_offsets_file: str,
+                                      output_sizes_file: str) -> None:
+    """``GenSparseMatrixBinFile`` with the encoding done on the current CUDA device; byte-identical output files."""
+    _check_file(library().FlashLLM_GenSparseMatrixBinFile_Device(
+        dense_file.encode(), M, K, nz_weights_file.encode(), tile_offsets_file.encode(), output_sizes_file.encode()),
+        "GenSparseMatrixBinFile_Device")
+
+
+def read_output_sizes(output_sizes_file: str) -> tuple[int, int]:
+    """``(NNZ, NumOffsets)`` of an ``.OutputSizes.bin`` file (reference csrc/SpMM_API.cu:536-541)."""
+    nnz, num_offsets = C.c_int(), C.c_int()
+    _check_file(library().FlashLLM_ReadOutputSizes(output_sizes_file.encode(), C.byref(nnz), C.byref(num_offsets)),
+                f"read {output_sizes_file}")
+    return nnz.value, num_offsets.value
+
+
+def read_sparse_matrix_bin_files(nz_weights_file: str, tile_offsets_file: str, nnz: int, num_offsets: int):
+    """The words and offsets of a converted matrix as numpy arrays, validated (the host half of FasterTransformer's
+    ``loadDataArrayFromBin``, reference third_party/ft.patch:3743-3790)."""
+    comp = np.empty(max(nnz, 1), np.uint32)
+    offs = np.empty(num_offsets, np.int32)
+    _check_file(library().FlashLLM_ReadSparseMatrixBinFiles(nz_weights_file.encode(), tile_offsets_file.encode(), nnz,
+                                                            num_offsets, comp.ctypes.data, offs.ctypes.data),
+                f"read {nz_weights_file} / {tile_offsets_file}")
+    return comp[:nnz], offs
+
+
+def load_sparse_matrix_bin_files(nz_weights_file: str, tile_offsets_file: str, nnz: int, num_offsets: int,
+                                 Compressed_A_d: int, TileOffsets_d: int) -> None:
+    """The same into device buffers (integer device pointers) of the caller, ready for ``SpMM_SplitK_API``."""
+    _check_file(library().FlashLLM_LoadSparseMatrixBinFiles(nz_weights_file.encode(), tile_offsets_file.encode(), nnz,
+                                                            num_offsets, Compressed_A_d, TileOffsets_d),
+                f"load {nz_weights_file} / {tile_offsets_file}")
+
+
+def write_rank_lists(model_dir: str, rank: int, nnz_list, num_offsets_list, split_k_list) -> None:
+    """``NNZ_List.<rank>.bin``, ``NumOffsets_List.<rank>.bin``, ``SplitK_List.<rank>.bin`` (reference
+    end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:188-195)."""
+    a, b, c = (np.ascontiguousarray(x, dtype=np.int32) for x in (nnz_list, num_offsets_list, split_k_list))
+    if not (a.shape == b.shape == c.shape and a.ndim == 1):
+        raise TypeError("the three lists must be one-dimensional and of equal length")
+    _check_file(library().FlashLLM_WriteRankLists(model_dir.encode(), rank, a.size, a.ctypes.data, b.ctypes.data,
+                                                  c.ctypes.data), f"write rank lists of rank {rank}")
+
+
+def read_rank_lists(model_dir: str, rank: int, entries: int):
+    """The three per-rank lists (``entries`` = 4 x decoder layers) as numpy int32 arrays."""
+    a, b, c = (np.empty(entries, np.int32) for _ in range(3))
+    _check_file(library().FlashLLM_ReadRankLists(model_dir.encode(), rank, entries, a.ctypes.data, b.ctypes.data,
+                                                 c.ctypes.data), f"read rank lists of rank {rank}")
+    return a, b, c
 
 
 # ----------------------------------------------------------------------------- device entry points

@@ -38,8 +38,8 @@ void count_launch()
 constexpr int kMaxDevices = 64;
 
 struct DeviceState {
-    std::once_flag once;
-    cudaError_t    init_error = cudaSuccess;
+    std::mutex     mutex;
+    bool           ready      = false;  // set once every step of the set-up has succeeded; a failed set-up is retried
     int            sm_count   = 0;
     int            smem_optin = 0;
     unsigned int*  status     = nullptr;
@@ -96,28 +96,33 @@ static DeviceState* device_state(cudaError_t* err)
         return nullptr;
     }
     DeviceState* st = &g_devices[dev];
-    std::call_once(st->once, [st, dev]() {
-        cudaError_t e = cudaDeviceGetAttribute(&st->sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (e == cudaSuccess)
-            e = cudaDeviceGetAttribute(&st->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        if (e == cudaSuccess)
-            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->status), g_status_word);
-        if (e == cudaSuccess)
-            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->noalloc_scratch), g_noalloc_scratch);
-        // The opt-in limit is a per-device property of each kernel; raise it once instead of on every call
-        // (the reference calls cudaFuncSetAttribute per launch, csrc/SpMM_API.cu:36-37).
-        if (e == cudaSuccess)
-            e = raise_smem_limit<16>(st->smem_optin);
-        if (e == cudaSuccess)
-            e = raise_smem_limit<32>(st->smem_optin);
-        if (e == cudaSuccess)
-            e = raise_smem_limit<64>(st->smem_optin);
-        if (e == cudaSuccess)
-            e = raise_smem_limit<128>(st->smem_optin);
-        st->init_error = e;
-    });
-    *err = st->init_error;
-    return *err == cudaSuccess ? st : nullptr;
+    std::lock_guard<std::mutex> lock(st->mutex);
+    if (st->ready) {
+        *err = cudaSuccess;
+        return st;
+    }
+    // Nothing here allocates.  A failure (for instance a first call made while a stream is being captured) is
+    // returned to this caller only; the next call tries again.
+    cudaError_t e = cudaDeviceGetAttribute(&st->sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess)
+        e = cudaDeviceGetAttribute(&st->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e == cudaSuccess)
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->status), g_status_word);
+    if (e == cudaSuccess)
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->noalloc_scratch), g_noalloc_scratch);
+    // The opt-in limit is a per-device property of each kernel; raise it once instead of on every call
+    // (the reference calls cudaFuncSetAttribute per launch, csrc/SpMM_API.cu:36-37).
+    if (e == cudaSuccess)
+        e = raise_smem_limit<16>(st->smem_optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit<32>(st->smem_optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit<64>(st->smem_optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit<128>(st->smem_optin);
+    st->ready = (e == cudaSuccess);
+    *err      = e;
+    return st->ready ? st : nullptr;
 }
 
 int device_status_pointer(unsigned int** status)
@@ -522,11 +527,13 @@ int FlashLLM_SpMM_SplitK_NoAlloc(void*       stream,
 {
     if (M <= 0 || N <= 0 || K <= 0 || Split_K < 1)
         return static_cast<int>(cudaErrorInvalidValue);
-    const unsigned long long need = 2ull * static_cast<unsigned long long>(Split_K) * M * N;  // Split_K fp16 matrices
+    // Split_K fp16 matrices, the room a caller-owned workspace would have; Split_K = 1 never touches the scratch
+    const unsigned long long need = Split_K > 1 ? 2ull * static_cast<unsigned long long>(Split_K) * M * N : 0ull;
     if (need > kNoAllocScratchBytes) {
         fprintf(stderr,
                 "FlashLLM_SpMM_SplitK_NoAlloc: Split_K*M*N*2 = %llu bytes exceeds the built-in %zu-byte scratch; lower "
-                "Split_K (1 needs none) or use FlashLLM_SpMM_SplitK with a workspace of your own.\n",
+                "Split_K (Split_K = 1 needs no scratch and is accepted at any size) or use FlashLLM_SpMM_SplitK with a "
+                "workspace of your own.\n",
                 need, kNoAllocScratchBytes);
         return static_cast<int>(cudaErrorInvalidValue);
     }

@@ -105,6 +105,60 @@ int FlashLLM_EncodeOnDevice_TileOffsets(void* stream, const void* A_d, int M, in
 int FlashLLM_EncodeOnDevice_Pack(void* stream, const void* A_d, int M, int K, const int* TileOffsets_d,
                                  uint32_t* Compressed_A_d, int reorder);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * On-disk format (the files of the reference's model converter).  `int` results: 0 ok, -1 a file cannot be opened
+ * or created, -2 a file is shorter than asked for, -3 the contents are not a well-formed tiled-CSL matrix,
+ * -4 bad arguments, positive = cudaError_t.
+ * ---------------------------------------------------------------------------------------------------------- */
+
+/* GenSparseMatrixBinFile with the encoding done on the current CUDA device (reference csrc/SpMM_API.cu:500-555 does
+ * it on one CPU thread; the reference's converter spreads matrices over processes instead,
+ * end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:147-156).  Same six arguments, byte-identical output
+ * files; allocates and frees its device buffers itself and returns a code instead of exiting. */
+int FlashLLM_GenSparseMatrixBinFile_Device(const char* DenseMatrixFileName,
+                                           int         M,
+                                           int         K,
+                                           const char* NZWeightsFileName,
+                                           const char* TileOffsetsFileName,
+                                           const char* OutputSizesFileName);
+
+/* Reads the {NNZ, NumOffsets} pair of an .OutputSizes.bin file (written at reference csrc/SpMM_API.cu:536-541, read
+ * back by huggingface_opt_convert_Phase2.py:160-165). */
+int FlashLLM_ReadOutputSizes(const char* OutputSizesFileName, int* NNZ, int* NumOffsets);
+
+/* Reads NNZ words of an .NZWeights.bin file and NumOffsets ints of a .TileOffsets.bin file into host buffers of the
+ * caller (the host half of FasterTransformer's loadDataArrayFromBin, reference third_party/ft.patch:3743-3790), and
+ * checks what that loader does not: offsets start at 0, never run backwards, stay within 2048 vectors per tile, end
+ * with the empty sentinel tile and add up to NNZ. */
+int FlashLLM_ReadSparseMatrixBinFiles(const char* NZWeightsFileName,
+                                      const char* TileOffsetsFileName,
+                                      int         NNZ,
+                                      int         NumOffsets,
+                                      uint32_t*   Compressed_A_h,
+                                      int*        TileOffsets_h);
+
+/* The same into device buffers of the caller, ready for SpMM_SplitK_API (reference third_party/ft.patch:1863-1965
+ * loads each decoder-layer matrix this way); synchronous copies on the current device. */
+int FlashLLM_LoadSparseMatrixBinFiles(const char* NZWeightsFileName,
+                                      const char* TileOffsetsFileName,
+                                      int         NNZ,
+                                      int         NumOffsets,
+                                      void*       Compressed_A_d,
+                                      int*        TileOffsets_d);
+
+/* The per-rank lists of a converted model directory: NNZ_List.<rank>.bin, NumOffsets_List.<rank>.bin and
+ * SplitK_List.<rank>.bin, `Entries` int32 each (4 per decoder layer, in the order QKV, attention output, FFN1, FFN2;
+ * a matrix left dense is recorded as 0/0/0).  Written at huggingface_opt_convert_Phase2.py:188-195, read by the
+ * patched FasterTransformer (third_party/ft.patch:2357-2359). */
+int FlashLLM_WriteRankLists(const char* ModelDir,
+                            int         Rank,
+                            int         Entries,
+                            const int*  NNZ_List,
+                            const int*  NumOffsets_List,
+                            const int*  SplitK_List);
+int FlashLLM_ReadRankLists(const char* ModelDir, int Rank, int Entries, int* NNZ_List, int* NumOffsets_List,
+                           int* SplitK_List);
+
 /* SpMM with the output epilogue of the reference's feed-forward call sites fused in (no counterpart in the reference
  * library: FasterTransformer runs add-bias + ReLU as a separate pass over C after the first FFN GEMM,
  * third_party/ft.patch ParallelGpt FFN layer): C[n][m] = act(sum_k A[m][k] * B[n][k] + bias[m]), computed on the fp32
@@ -131,10 +185,12 @@ int FlashLLM_SpMM_SplitK_BiasAct(void*       stream,
  * every GPU on which the library is loaded carries it until the process exits.
  *   - Same arguments and results as FlashLLM_SpMM_SplitK, minus `A` and `Reduction_Workspace`.
  *   - Split_K*M*N*2 bytes (what a caller-owned workspace would need) must not exceed 8 MiB; larger requests print
- *     a message to stderr and return cudaErrorInvalidValue.  Split_K = 1 never touches the scratch.
+ *     a message to stderr and return cudaErrorInvalidValue.  Split_K = 1 never touches the scratch and is accepted at
+ *     any size.
  *   - It calls no cudaMalloc, cudaFree or allocating library routine.  The first call on each device looks up the
  *     scratch's device address (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make that first
- *     call with the device current and before any stream capture begins.
+ *     call with the device current and before any stream capture begins.  If that set-up fails, the call returns the
+ *     error and the next call tries again.
  *   - All calls on a device share the one scratch array, which keeps the previous call's partial sums; every call
  *     overwrites the part it reads back, so nothing needs clearing, but two calls that overlap on the GPU (different
  *     streams, or graphs replayed concurrently) race on it.  Serialise them, or give the second one a workspace of

@@ -40,18 +40,22 @@ def test_no_alloc_entry_matches_workspace_entry(lib, oracle, M, K, N, split_k):
         lib.SpMM_SplitK_API(stream, None, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), want.data_ptr(), M, N, K,
                             ws.data_ptr(), split_k)
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        # Output buffers are made before the measurement, so that nothing torch does falls between the two readings
+        # of the driver's free-memory figure (cudaMemGetInfo), which also sees allocations made inside the library.
+        outs = [torch.full((N, M), float("nan"), dtype=torch.float16, device="cuda") for _ in range(3)]
+        lib.spmm_splitk_no_alloc(stream, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), outs[2].data_ptr(), M, N,
+                                 K, split_k)  # warm-up: the per-device set-up of the first call is behind us
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         for call in range(2):  # the second call finds the first call's partial sums in the scratch
-            got = torch.full((N, M), float("nan"), dtype=torch.float16, device="cuda")
-            base = torch.cuda.memory_allocated()
-            lib.spmm_splitk_no_alloc(stream, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), got.data_ptr(), M, N,
-                                     K, split_k)
-            torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == base
-            assert lib.consume_status() == 0
-            assert_close(got.cpu().numpy(), want.cpu().numpy().astype(np.float32), f"no-alloc call {call}")
-            assert_close(got.cpu().numpy(), oracle.gemm_f32(A, B), f"no-alloc call {call} vs host GEMM")
-        assert before <= torch.cuda.memory_allocated()
+            lib.spmm_splitk_no_alloc(stream, comp_d.data_ptr(), offs_d.data_ptr(), B_d.data_ptr(), outs[call].data_ptr(),
+                                     M, N, K, split_k)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "device memory was allocated during the calls"
+        assert lib.consume_status() == 0
+        for call in range(2):
+            assert_close(outs[call].cpu().numpy(), want.cpu().numpy().astype(np.float32), f"no-alloc call {call}")
+            assert_close(outs[call].cpu().numpy(), oracle.gemm_f32(A, B), f"no-alloc call {call} vs host GEMM")
     finally:
         lib.set_plan()
 
@@ -62,3 +66,7 @@ def test_no_alloc_entry_refuses_oversized_requests(lib, capfd):
     # 8 * 36864 * 16 * 2 bytes = 9.4 MB > 8 MiB
     assert L.FlashLLM_SpMM_SplitK_NoAlloc(None, fake, fake, fake, fake, 36864, 16, 9216, 8) == 1
     assert "exceeds the built-in" in capfd.readouterr().err
+    # without a K split the scratch is not used, so no size is too large for it: this request passes the size check and
+    # is turned down only later, for its null buffers
+    assert L.FlashLLM_SpMM_SplitK_NoAlloc(None, None, None, None, None, 36864, 128, 9216, 1) == 1
+    assert "exceeds the built-in" not in capfd.readouterr().err
