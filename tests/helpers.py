@@ -77,3 +77,20 @@ def random_problem(fl, M: int, K: int, N: int, sparsity: float, seed: int):
     A = fl.synthetic.sparse_uniform_matrix(M, K, sparsity, seed).numpy()
     B = fl.synthetic.dense_uniform_matrix(N, K, seed ^ 0xB).numpy()
     return A, B
+
+
+def assert_close_device(got: torch.Tensor, want: torch.Tensor, what: str = "", fp16_partials: int = 0) -> None:
+    """:func:`assert_close` for two device tensors of the same shape, evaluated on the device (whole outputs of the
+    full-size configurations: nothing is copied to the host but the two error figures)."""
+    assert got.shape == want.shape, f"{what}: shapes {tuple(got.shape)} vs {tuple(want.shape)}"
+    g, w = got.double(), want.double()
+    assert bool(torch.isfinite(w).all()) and bool(torch.isfinite(g).all()), f"{what}: non-finite outputs"
+    rms = float(torch.sqrt(torch.mean(w * w)))
+    peak = float(w.abs().max())
+    floor = max(0.05 * rms, 1e-30)
+    diff = (g - w).abs()
+    ab = float(diff.max()) / peak if peak > 0 else float(diff.max())
+    excess = torch.clamp(diff - fp16_partials * 2.0 ** -11 * peak, min=0.0) if fp16_partials else diff
+    rel = float((excess / torch.clamp(w.abs(), min=floor)).max())
+    assert rel <= REL_TOL and ab <= ABS_TOL_OF_MAX * (1 + fp16_partials), \
+        f"{what}: max rel err {rel:.3e}, max abs/peak {ab:.3e}"
