@@ -74,6 +74,21 @@ def run_chain(shape: ChainShape, x: torch.Tensor, matmul: Callable[..., torch.Te
     return all_reduce(matmul("ffn2", y1))                  # [N][H]
 
 
+def fp32_all_reduce(dist=None) -> Callable[[torch.Tensor], torch.Tensor]:
+    """The chain's collective: the ranks' fp16 partial matrices are widened, summed in fp32 (``dist.all_reduce``; NCCL
+    on GPUs, gloo on CPU) and rounded to fp16 once.  Summing the fp16 partials in fp16, as a plain all-reduce of the
+    SpMM outputs would, rounds after every addition: at eight ranks that alone put the layer output outside the
+    tolerance the chain is checked with.  ``dist=None`` (one rank) returns the identity."""
+    if dist is None:
+        return lambda t: t
+
+    def all_reduce(t: torch.Tensor) -> torch.Tensor:
+        wide = t.float()
+        dist.all_reduce(wide)
+        return wide.to(torch.float16)
+    return all_reduce
+
+
 def reference_chain(shape: ChainShape, x: torch.Tensor, w_qkv: torch.Tensor, w_out: torch.Tensor,
                     w_ffn1: torch.Tensor, w_ffn2: torch.Tensor) -> torch.Tensor:
     """The unsharded layer on the host in fp32, rounding to fp16 where the kernels store fp16 (every matmul output)."""

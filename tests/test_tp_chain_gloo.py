@@ -54,12 +54,7 @@ def _worker(rank: int, world: int, port: int, H: int, F: int, N: int, failures):
             out = torch.from_numpy(cpu_oracle.spmm_splitk(comp, offs, act.contiguous().numpy(), M, N, K, 1).copy())
             return torch.relu(out) if relu else out
 
-        def all_reduce(t):
-            acc = t.float()
-            dist.all_reduce(acc)
-            return acc.to(torch.float16)
-
-        got = tp_chain.run_chain(shape, x, matmul, all_reduce)
+        got = tp_chain.run_chain(shape, x, matmul, tp_chain.fp32_all_reduce(dist))  # the collective bench.py uses
         if rank == 0:
             want = tp_chain.reference_chain(shape, x, *full)
             from helpers import error_metrics

@@ -28,7 +28,8 @@ def test_chain_on_one_device_matches_the_host_layer(lib, oracle, H, F, world):
 
     def summed(name, inputs):
         parts = [c.matmul(name, inp).float().clone() for c, inp in zip(chains, inputs)]
-        return torch.stack(parts).sum(0).to(torch.float16)  # the all-reduce: fp32 sum of the fp16 partials
+        # what tp_chain.fp32_all_reduce does over the real ranks: fp32 sum of the fp16 partials, one rounding
+        return torch.stack(parts).sum(0).to(torch.float16)
 
     v = [c.matmul("qkv", x_d)[:, 2 * h:3 * h].contiguous() for c in chains]
     attn = summed("out_proj", v)
