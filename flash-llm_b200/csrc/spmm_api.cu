@@ -12,6 +12,7 @@
 #include "../../include/SpMM_API.cuh"
 #include "spmm_kernel_direct_sm100.cuh"
 #include "spmm_kernel_sm100.cuh"
+#include "spmm_kernel_stream_sm100.cuh"
 #include "tiled_csl_host.h"
 #include "tiling.h"
 
@@ -62,6 +63,19 @@ static std::once_flag g_encode_once;
 #endif
 constexpr int kDirectCapWide = 24, kDirectCapNarrow = FLASHLLM_NARROW_CAP;
 
+// Rows (32 vectors each) of the continuous-stream kernel's register window, for its three shapes: 4 or 6 scatter
+// warps with two CTAs per SM, 8 scatter warps with one CTA per SM.
+#ifndef FLASHLLM_STREAM_CAP4
+#define FLASHLLM_STREAM_CAP4 14
+#endif
+#ifndef FLASHLLM_STREAM_CAP6
+#define FLASHLLM_STREAM_CAP6 12
+#endif
+#ifndef FLASHLLM_STREAM_CAP8
+#define FLASHLLM_STREAM_CAP8 20
+#endif
+constexpr int kStreamCap4 = FLASHLLM_STREAM_CAP4, kStreamCap6 = FLASHLLM_STREAM_CAP6, kStreamCap8 = FLASHLLM_STREAM_CAP8;
+
 template<typename Kernel>
 static cudaError_t raise_smem_limit_of(Kernel kernel, int optin)
 {
@@ -82,6 +96,12 @@ static cudaError_t raise_smem_limit(int optin)
         e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapWide, 8, 1>, optin);
     if (e == cudaSuccess)
         e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, 2>, optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_of(spmm_tcgen05_stream_kernel<N_TILE, kStreamCap4, 4, 2>, optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_of(spmm_tcgen05_stream_kernel<N_TILE, kStreamCap6, 6, 2>, optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_of(spmm_tcgen05_stream_kernel<N_TILE, kStreamCap8, 8, 1>, optin);
     return e;
 }
 
@@ -166,7 +186,7 @@ static int n_tile_for(int N)
 
 static int plan_smem_bytes(const SpmmPlan& pl)
 {
-    const int bars = 8 * (2 * pl.ring_slots + 2 * pl.a_stages + 2 * pl.b_stages + 1) + 16 + 4 * pl.offsets_staged;
+    const int bars = 8 * (2 * pl.ring_slots + 3 * pl.a_stages + 2 * pl.b_stages + 1) + 16 + 4 * pl.offsets_staged;
     return pl.a_stages * kDenseTileBytes + pl.b_stages * pl.b_batch * pl.n_tile * kTileK * 2
            + pl.ring_slots * pl.chunk_vectors * 16 + bars;
 }
@@ -197,10 +217,11 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // Two pipelines per SM (4 scatter warps, 4 stages each) where they fit; wide-N tiles need the shared memory for
     // their B batches, so they run one deeper pipeline per SM instead.
     pl.path               = ov.v[kPlanPath] ? ov.v[kPlanPath] : kDefaultPath;
-    const bool direct     = pl.path == kPathDirect;
+    const bool stream     = pl.path == kPathStream;
+    const bool direct     = pl.path == kPathDirect || stream;  // both stream the words through registers
     pl.scatter_warps      = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps]
                                                     : (direct ? (pl.n_tile <= 64 ? 4 : 8) : (pl.n_tile <= 32 ? 4 : 8));
-    const bool two_per_sm = direct ? pl.scatter_warps == 4 : pl.n_tile <= 32;
+    const bool two_per_sm = direct ? pl.scatter_warps < 8 : pl.n_tile <= 32;
     pl.producers       = ov.v[kPlanProducers] ? ov.v[kPlanProducers] : 1;
     pl.chunk_vectors   = ov.v[kPlanChunkVectors] ? ov.v[kPlanChunkVectors] : 512;
     pl.ring_slots      = ov.v[kPlanRingSlots] ? ov.v[kPlanRingSlots]
@@ -218,7 +239,6 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
         pl.ring_slots    = 0;
         pl.chunk_vectors = 0;
     }
-
     // How to cut K.  A CTA that owns a whole tile row needs no reduction and pays its set-up and pipeline fill once,
     // so K is cut only to fill the GPU.  With `slots` CTAs resident at a time, G workspace parts per tile row run in
     // ceil(rows*G/slots) waves of CTAs that each process k_tiles/G tiles after a fixed cost worth about 16 tiles, and
@@ -270,6 +290,26 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // room for this CTA's slice of TileOffsets (K tiles of the longest part, plus one), up to 8 KB
     const int longest = (k_tiles + pl.cluster_k * pl.workspace_k - 1) / (pl.cluster_k * pl.workspace_k) + 1;
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
+    if (stream) {
+        // Stages beyond one per scatter warp let a warp go on with its next tile while the one it published is still
+        // being multiplied and cleared: half as many again where the shared memory of the SM (shared by two CTAs, or
+        // one) has room, an even number so that a stage is always served by the same MMA issuer.
+        pl.a_stages = pl.scatter_warps;
+        if (ov.v[kPlanAStages])
+            pl.a_stages = ov.v[kPlanAStages];
+        else {
+            const int per_cta = two_per_sm ? (st->smem_optin + 1024) / 2 - 1024 : st->smem_optin;
+            const int want    = (pl.scatter_warps + pl.scatter_warps / 2) / kDirectIssuers * kDirectIssuers;
+            for (int a = want; a > pl.scatter_warps; a -= kDirectIssuers) {
+                SpmmPlan trial = pl;
+                trial.a_stages = a;
+                if (a <= kMaxAStages && plan_smem_bytes(trial) <= per_cta) {
+                    pl.a_stages = a;
+                    break;
+                }
+            }
+        }
+    }
     pl.smem_bytes     = plan_smem_bytes(pl);
 
     const bool ring_ok = pl.scatter_warps >= 4 && pl.scatter_warps <= kMaxScatterWarps
@@ -282,7 +322,13 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
                          && pl.ring_slots * pl.chunk_vectors >= kMaxTileVectors + pl.chunk_vectors;
     const bool direct_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8)
                            && pl.a_stages == pl.scatter_warps && pl.b_batch % kDirectIssuers == 0;
-    const bool ok = (pl.path == kPathRing || pl.path == kPathDirect) && (direct ? direct_ok : ring_ok)
+    // a stage's successive tiles go to the same MMA issuer, and a warp never waits for a stage two uses ahead: both keep
+    // every mbarrier parity wait within one phase
+    const bool stream_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 6 || pl.scatter_warps == 8)
+                           && pl.a_stages >= pl.scatter_warps && pl.a_stages % kDirectIssuers == 0
+                           && pl.b_batch % kDirectIssuers == 0;
+    const bool ok = (pl.path == kPathRing || pl.path == kPathDirect || stream)
+                    && (stream ? stream_ok : (direct ? direct_ok : ring_ok))
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
                     && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
@@ -302,8 +348,9 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cudaLaunchConfig_t  cfg{};
     cudaLaunchAttribute attr[2];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
-    cfg.blockDim         = dim3((pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps
-                                                            : pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
+    cfg.blockDim         = dim3((pl.path == kPathStream   ? 2 + kDirectIssuers + pl.scatter_warps
+                                 : pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps
+                                                          : pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream           = stream;
     attr[0].id               = cudaLaunchAttributeClusterDimension;
@@ -318,6 +365,13 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
         cfg.numAttrs                                       = 2;
     }
     count_launch();
+    if (pl.path == kPathStream) {
+        if (pl.scatter_warps == 8)
+            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_stream_kernel<N_TILE, kStreamCap8, 8, 1>, tmap, params);
+        if (pl.scatter_warps == 6)
+            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_stream_kernel<N_TILE, kStreamCap6, 6, 2>, tmap, params);
+        return cudaLaunchKernelEx(&cfg, spmm_tcgen05_stream_kernel<N_TILE, kStreamCap4, 4, 2>, tmap, params);
+    }
     if (pl.path == kPathDirect) {
         if (pl.scatter_warps == 8)
             return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapWide, 8, 1>, tmap, params);

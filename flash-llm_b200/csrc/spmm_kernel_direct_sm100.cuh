@@ -116,8 +116,6 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
 
     // ---- set-up
     if (threadIdx.x == 0) {
-        // An earlier CTA that gave up leaves the status word set; later CTAs then skip their work.
-        const unsigned int status_now = *reinterpret_cast<volatile unsigned int*>(p.status);
         for (int i = 0; i < a_stages; ++i) {
             ptx::mbar_init(a_full + 8u * i, 1);
             ptx::mbar_init(a_empty + 8u * i, 1);
@@ -127,7 +125,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
             ptx::mbar_init(b_empty + 8u * i, MI);  // every issuer hands a batch back
         }
         ptx::mbar_init(acc_full, MI);
-        *abort_flag = (status_now != 0u) ? 1u : 0u;
+        abort_flag[0]             = 0u;  // a launch never inherits a give-up from an earlier one: the status word only reports
+        abort_flag[kDepsResolved] = 0u;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_b);
     }

@@ -44,6 +44,10 @@ struct SpmmParams {
 };
 
 constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
+// Word index, counted from a CTA's abort flag, of the flag its B loader sets once it is past griddepcontrol.wait.  With
+// launch overlap a CTA may sit behind its predecessor kernel for any length of time; the limit of the bounded waits is
+// meant for this CTA's own pipeline, so their clocks start only then.
+constexpr int kDepsResolved = 2;
 
 // Output epilogue shared by every place that rounds a finished fp32 sum to fp16: optional bias of output feature m,
 // optional ReLU.  (The reference's callers do this in a separate pass over fp16 C, third_party/ft.patch
@@ -111,6 +115,10 @@ wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsig
         if ((it & 1023u) == 0u) {
             if (*abort_flag)
                 return false;
+            if (abort_flag[kDepsResolved] == 0u) {  // still behind the previous kernel of the stream: no clock yet
+                t0 = 0;
+                continue;
+            }
             const uint64_t now = ptx::globaltimer_ns();
             if (t0 == 0)
                 t0 = now;
@@ -138,6 +146,10 @@ wait_bounded_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_fla
         if ((it & 1023u) == 0u) {
             if (*abort_flag)
                 return false;
+            if (abort_flag[kDepsResolved] == 0u) {  // still behind the previous kernel of the stream: no clock yet
+                t0 = 0;
+                continue;
+            }
             const uint64_t now = ptx::globaltimer_ns();
             if (t0 == 0)
                 t0 = now;
@@ -220,6 +232,7 @@ __device__ __forceinline__ void load_b_batches(const CUtensorMap* tmap, int batc
                                                volatile uint32_t* abort_flag, unsigned int* status)
 {
     ptx::grid_dependency_wait();
+    abort_flag[kDepsResolved] = 1u;
     int      bs     = 0;
     uint32_t use    = 0;
     int      issued = 0;
@@ -441,8 +454,6 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 
     // ---- set-up
     if (threadIdx.x == 0) {
-        // An earlier CTA that gave up leaves the status word set; later CTAs then skip their work.
-        const unsigned int status_now = *reinterpret_cast<volatile unsigned int*>(p.status);
         for (int i = 0; i < ring_slots; ++i) {
             ptx::mbar_init(ring_full + 8u * i, 1);
             // a slot is free again once every one of its CV vectors has been consumed: the warps that consume them
@@ -458,8 +469,9 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
             ptx::mbar_init(b_empty + 8u * i, 1);
         }
         ptx::mbar_init(acc_full, 1);
-        *abort_flag      = (status_now != 0u) ? 1u : 0u;
-        *tiles_scattered = 0;
+        abort_flag[0]             = 0u;  // a launch never inherits a give-up from an earlier one: the status word only reports
+        abort_flag[kDepsResolved] = 0u;
+        *tiles_scattered          = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_b);
     }
