@@ -634,37 +634,50 @@ def run_tp_chain(args) -> None:
     x = fl.synthetic.normal_matrix(N_TOKENS, H, 1.0, seed + 9, device=dev).to(torch.float16)
     fl.set_launch_overlap(True)
     all_reduce = tp_chain.fp32_all_reduce(ranks.dist if world > 1 else None)
+    # The row-parallel layers go through the library's fused SpMM + all-reduce (peer stores, no NCCL on the data path);
+    # --nccl-chain keeps the plain SpMM followed by an NCCL all-reduce, which is also timed beside it as the baseline.
+    group = tp_chain.PeerGroup(fl, ranks.dist, rank, world, N_TOKENS * H) if world > 1 else None
+    fused = group is not None and not args.nccl_chain
+    step_nccl = lambda: chain.step(x, all_reduce)  # noqa: E731
+    step = (lambda: chain.step(x, comm=group.comm)) if fused else step_nccl
 
     # ---- parity of the sharded chain over the real collective against the unsharded layer on the host (rank 0)
-    out = chain.step(x, all_reduce).clone()
-    torch.cuda.synchronize(dev)
-    status = fl.consume_status()
-    assert status == 0, f"kernel status {status:#x}"
-    parity = [0.0, 0.0]
-    if rank == 0:
-        want = tp_chain.reference_chain(shape, x.cpu(), *[w.cpu() for w in full])
-        got = out.cpu().float()
-        rms = float(want.pow(2).mean().sqrt())
-        parity = [float(((got - want).abs() / want.abs().clamp_min(0.05 * rms)).max()),
-                  float((got - want).abs().max() / want.abs().max())]
-    parity = ranks.max(parity)  # every rank learns rank 0's figures and fails together
-    assert parity[0] <= CHAIN_REL_TOL and parity[1] <= CHAIN_ABS_TOL_OF_MAX, \
-        f"chain output differs from the host layer: rel {parity[0]:.3e}, abs/peak {parity[1]:.3e}"
+    want = tp_chain.reference_chain(shape, x.cpu(), *[w.cpu() for w in full]) if rank == 0 else None
     del full
+
+    def parity_of(run_step) -> list:
+        out = run_step().clone()
+        torch.cuda.synchronize(dev)
+        status = fl.consume_status()
+        assert status == 0, f"kernel status {status:#x}"
+        figures = [0.0, 0.0]
+        if rank == 0:
+            got = out.cpu().float()
+            rms = float(want.pow(2).mean().sqrt())
+            figures = [float(((got - want).abs() / want.abs().clamp_min(0.05 * rms)).max()),
+                       float((got - want).abs().max() / want.abs().max())]
+        figures = ranks.max(figures)  # every rank learns rank 0's figures and fails together
+        assert figures[0] <= CHAIN_REL_TOL and figures[1] <= CHAIN_ABS_TOL_OF_MAX, \
+            f"chain output differs from the host layer: rel {figures[0]:.3e}, abs/peak {figures[1]:.3e}"
+        return figures
+    parity = parity_of(step)
+    parity_nccl = parity_of(step_nccl) if fused else parity
 
     steps = args.steps
     for _ in range(max(args.warmup, 3)):
-        chain.step(x, all_reduce)
+        step()
     ranks.barrier()
     before = fl.launch_count()
-    chain.step(x, all_reduce)
+    step()
     launches_per_step = fl.launch_count() - before
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
         t_begin = time.time()
-        ms, reps = timed_repetitions(lambda: chain.step(x, all_reduce), steps, dev, ranks)
+        ms, reps = timed_repetitions(step, steps, dev, ranks)
         clocks.mark(t_begin, time.time())
         time.sleep(0.05)
-    # the same kernels without the collectives (every rank on its own partial sums), and the collective on its own
+    # the NCCL form of the chain, the same kernels without any collective (every rank on its own partial sums), and
+    # the NCCL collective on its own
+    ms_nccl = timed_repetitions(step_nccl, steps, dev, ranks, TIMED_REGION_S / 3)[0] if fused else ms
     ms_local, _ = timed_repetitions(lambda: chain.step(x, lambda t: t), steps, dev, ranks, TIMED_REGION_S / 3)
     buf = torch.zeros((N_TOKENS, H), dtype=torch.float16, device=dev)
     ms_coll = timed_repetitions(lambda: all_reduce(buf), steps, dev, ranks, TIMED_REGION_S / 3)[0] if world > 1 else 0.0
@@ -680,16 +693,24 @@ def run_tp_chain(args) -> None:
             "config": {"workload": "tensor-parallel sparse layer chain, OPT-66B dimensions (H=9216, F=36864), N=16, "
                                    "N(0,0.02) weights magnitude-pruned to 80 % per matrix, activations N(0,1): QKV -> "
                                    "out-proj -> all-reduce -> FFN1 -> ReLU -> FFN2 -> all-reduce",
-                       "parallelism": f"tp{world}: QKV/FFN1 column-parallel, out-proj/FFN2 row-parallel, NCCL all-reduce "
-                                      f"of {N_TOKENS}x{H} (fp32 sum of fp16 partials) after each row-parallel SpMM",
+                       "parallelism": f"tp{world}: QKV/FFN1 column-parallel, out-proj/FFN2 row-parallel; " +
+                                      ("row-parallel SpMM with the all-reduce fused in: fp32 partial sums stored into "
+                                       "every rank's receive buffer over NVLink, summed in rank order, one rounding"
+                                       if fused else
+                                       f"NCCL all-reduce of {N_TOKENS}x{H} (fp32 sum of fp16 partials) after each "
+                                       "row-parallel SpMM"),
                        "shards": {k: list(v) for k, v in shape.shard_shapes().items()},
                        "timing": f"median of {reps} repetitions of exactly {steps} steps"},
+            "ms_per_step_nccl_chain": ms_nccl / steps,
             "ms_per_step_without_collectives": ms_local / steps,
-            "ms_per_all_reduce_alone": ms_coll / steps,
+            "ms_per_nccl_all_reduce_alone": ms_coll / steps,
             "hbm_gbs_per_gpu": bytes_alg * steps / (ms * 1e-3) / 1e9,
             "parity_vs_host_layer": {"max_rel_err_floor_5pct_rms": parity[0], "max_abs_over_peak": parity[1],
-                                     "asserted": [CHAIN_REL_TOL, CHAIN_ABS_TOL_OF_MAX]},
+                                     "nccl_chain": parity_nccl, "asserted": [CHAIN_REL_TOL, CHAIN_ABS_TOL_OF_MAX]},
             "gpu_launches": launches_per_step * steps, "clocks": clocks.summary()}), flush=True)
+    if group is not None:
+        ranks.barrier()  # nobody frees a buffer while a peer may still store into it
+        group.close()
     ranks.close()
 
 
@@ -701,6 +722,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cpu"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="skip the sweep, encoder and CPU-baseline sub-records")
+    ap.add_argument("--nccl-chain", action="store_true",
+                    help="tp-chain: plain SpMM + NCCL all-reduce for the row-parallel layers instead of the fused call")
     ap.add_argument("--workload", default="layer", choices=["layer", "tp-chain"],
                     help="layer: the four OPT-66B SpMMs, weight rows sharded, no collective (the headline metric); "
                          "tp-chain: the tensor-parallel layer chain with all-reduces")

@@ -14,6 +14,12 @@ from .api import (  # noqa: F401
     InitSparseMatrixA_API_NoReorder,
     SpMM_SplitK_API,
     build_library,
+    comm_alloc_buffer,
+    comm_close_peer_buffer,
+    comm_create,
+    comm_destroy,
+    comm_free_buffer,
+    comm_open_peer_buffer,
     consume_status,
     encode_on_device,
     gen_sparse_matrix_bin_file_device,
@@ -28,6 +34,7 @@ from .api import (  # noqa: F401
     set_plan,
     splitk_reduction,
     spmm_splitk_bias_act,
+    spmm_splitk_allreduce,
     spmm_splitk_no_alloc,
     write_rank_lists,
 )

@@ -74,6 +74,20 @@ def library() -> C.CDLL:
         f.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
     L.FlashLLM_SpMM_SplitK_NoAlloc.restype = C.c_int
     L.FlashLLM_SpMM_SplitK_NoAlloc.argtypes = [C.c_void_p] * 5 + [C.c_int] * 4
+    L.FlashLLM_Comm_BufferBytes.restype = C.c_ulonglong
+    L.FlashLLM_Comm_BufferBytes.argtypes = [C.c_int, C.c_longlong]
+    L.FlashLLM_Comm_AllocBuffer.restype = C.c_int
+    L.FlashLLM_Comm_AllocBuffer.argtypes = [C.c_int, C.c_longlong, C.POINTER(C.c_void_p), C.c_void_p]
+    L.FlashLLM_Comm_OpenPeerBuffer.restype = C.c_int
+    L.FlashLLM_Comm_OpenPeerBuffer.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    for name in ("FlashLLM_Comm_ClosePeerBuffer", "FlashLLM_Comm_FreeBuffer", "FlashLLM_Comm_Destroy"):
+        f = getattr(L, name)
+        f.restype = C.c_int
+        f.argtypes = [C.c_void_p]
+    L.FlashLLM_Comm_Create.restype = C.c_int
+    L.FlashLLM_Comm_Create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_longlong, C.POINTER(C.c_void_p)]
+    L.FlashLLM_SpMM_SplitK_AllReduce.restype = C.c_int
+    L.FlashLLM_SpMM_SplitK_AllReduce.argtypes = [C.c_void_p] * 6 + [C.c_int] * 3 + [C.c_void_p, C.c_int, C.c_int]
     L.FlashLLM_SplitK_Reduction.restype = C.c_int
     L.FlashLLM_SplitK_Reduction.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
     L.FlashLLM_SetLaunchOverlap.argtypes = [C.c_int]
@@ -233,6 +247,62 @@ def spmm_splitk_no_alloc(stream: int, Compressed_A: int, TileOffsets: int, B: in
     that array and race; the first call on a device should precede any stream capture."""
     code = library().FlashLLM_SpMM_SplitK_NoAlloc(stream, Compressed_A, TileOffsets, B, C_out, M, N, K, Split_K)
     _check(code, f"SpMM_SplitK_NoAlloc(M={M}, N={N}, K={K}, Split_K={Split_K})")
+
+
+# ----------------------------------------------------------------------------- fused row-parallel SpMM + all-reduce
+
+IPC_HANDLE_BYTES = 64  # sizeof(cudaIpcMemHandle_t)
+
+
+def comm_alloc_buffer(world: int, max_elems: int) -> tuple[int, bytes]:
+    """This GPU's receive buffer for a group of ``world`` GPUs and outputs of up to ``max_elems`` (= M*N) values:
+    ``(device pointer, inter-process handle)``.  The handle is what the other ranks pass to
+    :func:`comm_open_peer_buffer`."""
+    ptr = C.c_void_p()
+    handle = C.create_string_buffer(IPC_HANDLE_BYTES)
+    _check(library().FlashLLM_Comm_AllocBuffer(world, max_elems, C.byref(ptr), handle), "Comm_AllocBuffer")
+    return int(ptr.value), handle.raw
+
+
+def comm_open_peer_buffer(handle: bytes) -> int:
+    """Maps another rank's receive buffer (its :func:`comm_alloc_buffer` handle) into this process."""
+    ptr = C.c_void_p()
+    _check(library().FlashLLM_Comm_OpenPeerBuffer(C.create_string_buffer(handle, IPC_HANDLE_BYTES), C.byref(ptr)),
+           "Comm_OpenPeerBuffer")
+    return int(ptr.value)
+
+
+def comm_close_peer_buffer(ptr: int) -> None:
+    _check(library().FlashLLM_Comm_ClosePeerBuffer(ptr), "Comm_ClosePeerBuffer")
+
+
+def comm_free_buffer(ptr: int) -> None:
+    _check(library().FlashLLM_Comm_FreeBuffer(ptr), "Comm_FreeBuffer")
+
+
+def comm_create(rank: int, world: int, max_elems: int, buffers: list[int]):
+    """A communicator for :func:`spmm_splitk_allreduce`: ``buffers[w]`` is rank w's receive buffer as mapped in this
+    process (``buffers[rank]`` the own one).  Every rank must make the same sequence of fused calls on it."""
+    comm = C.c_void_p()
+    arr = (C.c_void_p * world)(*buffers)
+    _check(library().FlashLLM_Comm_Create(C.byref(comm), rank, world, max_elems, arr), "Comm_Create")
+    return comm
+
+
+def comm_destroy(comm) -> None:
+    library().FlashLLM_Comm_Destroy(comm)
+
+
+def spmm_splitk_allreduce(comm, stream: int, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int, N: int,
+                          K: int, bias: int | None = None, activation: int = ACT_NONE, phases: int = 3) -> None:
+    """Row-parallel SpMM with the all-reduce fused in: ``C[N][M] = act(sum over the group of (B_w @ A_w^T) + bias)``,
+    where this rank holds the K slice ``A_w[M][K]``, ``B_w[N][K]``.  Every rank's kernel stores its fp32 partial sums
+    straight into all ranks' receive buffers; a second kernel adds them in rank order and rounds once, so every rank
+    ends with the same bits.  ``phases``: 3 = both kernels (the normal call), 1 = the SpMM and its stores only,
+    2 = the summing kernel only (for driving several ranks from one stream: all ranks' phase 1, then their phase 2)."""
+    code = library().FlashLLM_SpMM_SplitK_AllReduce(comm, stream, Compressed_A, TileOffsets, B, C_out, M, N, K, bias,
+                                                    activation, phases)
+    _check(code, f"SpMM_SplitK_AllReduce(M={M}, N={N}, K={K})")
 
 
 def splitk_reduction(stream: int, C_out: int, workspace: int, M: int, N: int, split_k: int) -> None:

@@ -8,11 +8,12 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <new>
 
 #include "../../include/SpMM_API.cuh"
 #include "spmm_kernel_direct_sm100.cuh"
 #include "spmm_kernel_sm100.cuh"
-#include "spmm_kernel_stream_sm100.cuh"
+#include "spmm_kernel_janitor_sm100.cuh"
 #include "tiled_csl_host.h"
 #include "tiling.h"
 
@@ -65,16 +66,16 @@ constexpr int kDirectCapWide = 24, kDirectCapNarrow = FLASHLLM_NARROW_CAP;
 
 // Rows (32 vectors each) of the continuous-stream kernel's register window, for its three shapes: 4 or 6 scatter
 // warps with two CTAs per SM, 8 scatter warps with one CTA per SM.
-#ifndef FLASHLLM_STREAM_CAP4
-#define FLASHLLM_STREAM_CAP4 14
+#ifndef FLASHLLM_JANITOR_CAP4
+#define FLASHLLM_JANITOR_CAP4 14
 #endif
-#ifndef FLASHLLM_STREAM_CAP6
-#define FLASHLLM_STREAM_CAP6 12
+#ifndef FLASHLLM_JANITOR_CAP6
+#define FLASHLLM_JANITOR_CAP6 14
 #endif
-#ifndef FLASHLLM_STREAM_CAP8
-#define FLASHLLM_STREAM_CAP8 20
+#ifndef FLASHLLM_JANITOR_CAP8
+#define FLASHLLM_JANITOR_CAP8 20
 #endif
-constexpr int kStreamCap4 = FLASHLLM_STREAM_CAP4, kStreamCap6 = FLASHLLM_STREAM_CAP6, kStreamCap8 = FLASHLLM_STREAM_CAP8;
+constexpr int kJanitorCap4 = FLASHLLM_JANITOR_CAP4, kJanitorCap6 = FLASHLLM_JANITOR_CAP6, kJanitorCap8 = FLASHLLM_JANITOR_CAP8;
 
 template<typename Kernel>
 static cudaError_t raise_smem_limit_of(Kernel kernel, int optin)
@@ -97,11 +98,11 @@ static cudaError_t raise_smem_limit(int optin)
     if (e == cudaSuccess)
         e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, 2>, optin);
     if (e == cudaSuccess)
-        e = raise_smem_limit_of(spmm_tcgen05_stream_kernel<N_TILE, kStreamCap4, 4, 2>, optin);
+        e = raise_smem_limit_of(spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap4, 4, 2>, optin);
     if (e == cudaSuccess)
-        e = raise_smem_limit_of(spmm_tcgen05_stream_kernel<N_TILE, kStreamCap6, 6, 2>, optin);
+        e = raise_smem_limit_of(spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap6, 6, 2>, optin);
     if (e == cudaSuccess)
-        e = raise_smem_limit_of(spmm_tcgen05_stream_kernel<N_TILE, kStreamCap8, 8, 1>, optin);
+        e = raise_smem_limit_of(spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap8, 8, 1>, optin);
     return e;
 }
 
@@ -217,8 +218,8 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // Two pipelines per SM (4 scatter warps, 4 stages each) where they fit; wide-N tiles need the shared memory for
     // their B batches, so they run one deeper pipeline per SM instead.
     pl.path               = ov.v[kPlanPath] ? ov.v[kPlanPath] : kDefaultPath;
-    const bool stream     = pl.path == kPathStream;
-    const bool direct     = pl.path == kPathDirect || stream;  // both stream the words through registers
+    const bool janitor    = pl.path == kPathJanitor;
+    const bool direct     = pl.path == kPathDirect || janitor;  // both stream the words through registers
     pl.scatter_warps      = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps]
                                                     : (direct ? (pl.n_tile <= 64 ? 4 : 8) : (pl.n_tile <= 32 ? 4 : 8));
     const bool two_per_sm = direct ? pl.scatter_warps < 8 : pl.n_tile <= 32;
@@ -290,7 +291,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // room for this CTA's slice of TileOffsets (K tiles of the longest part, plus one), up to 8 KB
     const int longest = (k_tiles + pl.cluster_k * pl.workspace_k - 1) / (pl.cluster_k * pl.workspace_k) + 1;
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
-    if (stream) {
+    if (janitor) {
         // Stages beyond one per scatter warp let a warp go on with its next tile while the one it published is still
         // being multiplied and cleared: half as many again where the shared memory of the SM (shared by two CTAs, or
         // one) has room, an even number so that a stage is always served by the same MMA issuer.
@@ -324,11 +325,11 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
                            && pl.a_stages == pl.scatter_warps && pl.b_batch % kDirectIssuers == 0;
     // a stage's successive tiles go to the same MMA issuer, and a warp never waits for a stage two uses ahead: both keep
     // every mbarrier parity wait within one phase
-    const bool stream_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 6 || pl.scatter_warps == 8)
+    const bool janitor_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 6 || pl.scatter_warps == 8)
                            && pl.a_stages >= pl.scatter_warps && pl.a_stages % kDirectIssuers == 0
                            && pl.b_batch % kDirectIssuers == 0;
-    const bool ok = (pl.path == kPathRing || pl.path == kPathDirect || stream)
-                    && (stream ? stream_ok : (direct ? direct_ok : ring_ok))
+    const bool ok = (pl.path == kPathRing || pl.path == kPathDirect || janitor)
+                    && (janitor ? janitor_ok : (direct ? direct_ok : ring_ok))
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
                     && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
@@ -348,7 +349,7 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cudaLaunchConfig_t  cfg{};
     cudaLaunchAttribute attr[2];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
-    cfg.blockDim         = dim3((pl.path == kPathStream   ? 2 + kDirectIssuers + pl.scatter_warps
+    cfg.blockDim         = dim3((pl.path == kPathJanitor   ? 2 + kDirectIssuers + pl.scatter_warps
                                  : pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps
                                                           : pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
@@ -365,12 +366,12 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
         cfg.numAttrs                                       = 2;
     }
     count_launch();
-    if (pl.path == kPathStream) {
+    if (pl.path == kPathJanitor) {
         if (pl.scatter_warps == 8)
-            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_stream_kernel<N_TILE, kStreamCap8, 8, 1>, tmap, params);
+            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap8, 8, 1>, tmap, params);
         if (pl.scatter_warps == 6)
-            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_stream_kernel<N_TILE, kStreamCap6, 6, 2>, tmap, params);
-        return cudaLaunchKernelEx(&cfg, spmm_tcgen05_stream_kernel<N_TILE, kStreamCap4, 4, 2>, tmap, params);
+            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap6, 6, 2>, tmap, params);
+        return cudaLaunchKernelEx(&cfg, spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap4, 4, 2>, tmap, params);
     }
     if (pl.path == kPathDirect) {
         if (pl.scatter_warps == 8)
@@ -421,6 +422,31 @@ static bool n_supported(int N)
 
 using namespace flashllm;
 
+// Receive buffers of a GPU group for the fused row-parallel SpMM + all-reduce.  Every GPU owns one buffer with two
+// sets (used by alternate calls) of `world` fp32 slots [max_elems] and `world` x kCommFlagsPerRank flag words:
+//   [set 0 slots][set 1 slots][set 0 flags][set 1 flags]
+// Slot w / flag row w of a GPU's buffer is written only by GPU w.  While one call's sums are still being read on a
+// slow GPU, a fast GPU's next call writes the other set; it cannot start the call after that before the slow GPU has
+// taken part in the next one, so two sets are enough.
+constexpr int kCommFlagsPerRank = 8192;
+
+struct FlashLLMComm {
+    int            rank = 0, world = 0;
+    long long      max_elems = 0;
+    unsigned char* buffer[kMaxPushWorld] = {nullptr};  // buffer[w]: GPU w's receive buffer as mapped in this process
+    unsigned int   epoch = 0;                          // calls made so far; every GPU of the group makes the same calls
+};
+
+static size_t comm_slot_bytes(int world, long long max_elems)
+{
+    return static_cast<size_t>(world) * static_cast<size_t>(max_elems) * sizeof(float);
+}
+
+static size_t comm_buffer_bytes(int world, long long max_elems)
+{
+    return 2 * comm_slot_bytes(world, max_elems) + 2 * static_cast<size_t>(world) * kCommFlagsPerRank * sizeof(unsigned int);
+}
+
 // SpMM_SplitK_API plus the output epilogue (bias of output feature m, activation) the public entry points select.
 static cudaError_t spmm_launch_all(cudaStream_t stream,
                                    const uint4* Compressed_A,
@@ -433,7 +459,9 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
                                    half*        Reduction_Workspace,
                                    int          Split_K,
                                    const half*  bias,
-                                   int          activation)
+                                   int          activation,
+                                   FlashLLMComm* comm = nullptr,
+                                   int           phases = 3)
 {
     if (!n_supported(N_Global)) {
         printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
@@ -453,9 +481,12 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
         return err;
 
     SpmmParams params{};
-    if ((err = make_plan(st, M_Global, N_Global, K_Global, Split_K, &params.plan)) != cudaSuccess)
+    if ((err = make_plan(st, M_Global, N_Global, K_Global, comm ? 1 : Split_K, &params.plan)) != cudaSuccess)
         return err;
     SpmmPlan& pl = params.plan;
+    if (comm && pl.workspace_k != 1)
+        return cudaErrorInvalidConfiguration;  // a pinned plan asked for workspace parts: partial sums must leave the
+                                               // kernel complete to be pushed
     // The partial-matrix pass reads 16-byte groups of the workspace and writes 8-byte groups of C.
     if (pl.workspace_k > 1
         && ((reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u) != 0 || (reinterpret_cast<uintptr_t>(C) & 7u) != 0))
@@ -490,14 +521,60 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
 
     const int tile_rows = M_Global / kTileM;
     const int n_tiles   = (N_Global + pl.n_tile - 1) / pl.n_tile;
-    switch (pl.n_tile) {
-        case 16: err = launch_spmm<16>(stream, tmap, params, tile_rows, n_tiles); break;
-        case 32: err = launch_spmm<32>(stream, tmap, params, tile_rows, n_tiles); break;
-        case 64: err = launch_spmm<64>(stream, tmap, params, tile_rows, n_tiles); break;
-        default: err = launch_spmm<128>(stream, tmap, params, tile_rows, n_tiles); break;
+    const int grid_ctas = pl.cluster_k * tile_rows * n_tiles * pl.workspace_k;
+    size_t    set_slots = 0, set_flags = 0;
+    if (comm) {
+        const long long elems = static_cast<long long>(M_Global) * N_Global;
+        if (elems > comm->max_elems || elems % 4 != 0 || grid_ctas > kCommFlagsPerRank
+            || (reinterpret_cast<uintptr_t>(C) & 7u) != 0)
+            return cudaErrorInvalidValue;
+        if (phases & 1)
+            comm->epoch += 1;  // a new call; a sum-only call belongs to the call whose stores went out last
+        const int set       = static_cast<int>(comm->epoch & 1u);
+        set_slots           = static_cast<size_t>(set) * comm_slot_bytes(comm->world, comm->max_elems);
+        set_flags           = 2 * comm_slot_bytes(comm->world, comm->max_elems)
+                    + static_cast<size_t>(set) * comm->world * kCommFlagsPerRank * sizeof(unsigned int);
+        params.push_world   = comm->world;
+        params.push_epoch   = comm->epoch;
+        for (int w = 0; w < comm->world; ++w) {
+            params.push_slot[w] = reinterpret_cast<float*>(comm->buffer[w] + set_slots) + comm->rank * comm->max_elems;
+            params.push_flag[w] = reinterpret_cast<unsigned int*>(comm->buffer[w] + set_flags) + comm->rank * kCommFlagsPerRank;
+        }
     }
-    if (err != cudaSuccess)
-        return err;
+    if (!comm || (phases & 1)) {
+        switch (pl.n_tile) {
+            case 16: err = launch_spmm<16>(stream, tmap, params, tile_rows, n_tiles); break;
+            case 32: err = launch_spmm<32>(stream, tmap, params, tile_rows, n_tiles); break;
+            case 64: err = launch_spmm<64>(stream, tmap, params, tile_rows, n_tiles); break;
+            default: err = launch_spmm<128>(stream, tmap, params, tile_rows, n_tiles); break;
+        }
+        if (err != cudaSuccess)
+            return err;
+    }
+    if (comm && !(phases & 2))
+        return cudaSuccess;
+    if (comm) {
+        // second kernel: waits (bounded) for every GPU's flags of this call, then adds the slots up in rank order
+        const long long     count   = static_cast<long long>(M_Global) * N_Global;
+        const int           threads = 256;
+        const unsigned      blocks  = static_cast<unsigned>((count / 4 + threads - 1) / threads);
+        cudaLaunchConfig_t  cfg{};
+        cudaLaunchAttribute attr[1];
+        cfg.gridDim  = dim3(blocks, 1, 1);
+        cfg.blockDim = dim3(threads, 1, 1);
+        cfg.stream   = stream;
+        if (g_launch_overlap.load(std::memory_order_relaxed)) {
+            attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs                                          = attr;
+            cfg.numAttrs                                       = 1;
+        }
+        unsigned char* mine = comm->buffer[comm->rank];
+        count_launch();
+        return cudaLaunchKernelEx(&cfg, allreduce_sum_kernel, C, reinterpret_cast<const float*>(mine + set_slots),
+                                  comm->max_elems, reinterpret_cast<const unsigned int*>(mine + set_flags), kCommFlagsPerRank,
+                                  comm->epoch, comm->world, grid_ctas, count, bias, M_Global, activation, st->status);
+    }
     if (pl.workspace_k > 1)
         return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k,
                                bias, M_Global, activation);
@@ -599,6 +676,93 @@ int FlashLLM_SpMM_SplitK_NoAlloc(void*       stream,
                                             static_cast<const uint4*>(Compressed_A), TileOffsets,
                                             static_cast<const half*>(B), static_cast<half*>(C), M, N, K,
                                             reinterpret_cast<half*>(st->noalloc_scratch), Split_K));
+}
+
+unsigned long long FlashLLM_Comm_BufferBytes(int world, long long max_elems)
+{
+    if (world < 1 || world > kMaxPushWorld || max_elems < 4)
+        return 0;
+    return comm_buffer_bytes(world, max_elems);
+}
+
+int FlashLLM_Comm_AllocBuffer(int world, long long max_elems, void** buffer, void* ipc_handle)
+{
+    if (buffer == nullptr || world < 1 || world > kMaxPushWorld || max_elems < 4 || max_elems % 4 != 0)
+        return static_cast<int>(cudaErrorInvalidValue);
+    const size_t bytes = comm_buffer_bytes(world, max_elems);
+    cudaError_t  e     = cudaMalloc(buffer, bytes);
+    if (e == cudaSuccess)
+        e = cudaMemset(*buffer, 0, bytes);  // flags start below every epoch
+    if (e == cudaSuccess && ipc_handle != nullptr)
+        e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(ipc_handle), *buffer);
+    if (e == cudaSuccess)
+        e = cudaDeviceSynchronize();
+    return static_cast<int>(e);
+}
+
+int FlashLLM_Comm_OpenPeerBuffer(const void* ipc_handle, void** buffer)
+{
+    if (ipc_handle == nullptr || buffer == nullptr)
+        return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(cudaIpcOpenMemHandle(buffer, *static_cast<const cudaIpcMemHandle_t*>(ipc_handle),
+                                                 cudaIpcMemLazyEnablePeerAccess));
+}
+
+int FlashLLM_Comm_ClosePeerBuffer(void* buffer)
+{
+    return static_cast<int>(cudaIpcCloseMemHandle(buffer));
+}
+
+int FlashLLM_Comm_FreeBuffer(void* buffer)
+{
+    return static_cast<int>(cudaFree(buffer));
+}
+
+int FlashLLM_Comm_Create(void** comm, int rank, int world, long long max_elems, void* const* buffers)
+{
+    if (comm == nullptr || buffers == nullptr || world < 1 || world > kMaxPushWorld || rank < 0 || rank >= world
+        || max_elems < 4 || max_elems % 4 != 0)
+        return static_cast<int>(cudaErrorInvalidValue);
+    for (int w = 0; w < world; ++w)
+        if (buffers[w] == nullptr || (reinterpret_cast<uintptr_t>(buffers[w]) & 15u) != 0)
+            return static_cast<int>(cudaErrorInvalidValue);
+    FlashLLMComm* c = new (std::nothrow) FlashLLMComm();
+    if (c == nullptr)
+        return static_cast<int>(cudaErrorMemoryAllocation);
+    c->rank      = rank;
+    c->world     = world;
+    c->max_elems = max_elems;
+    for (int w = 0; w < world; ++w)
+        c->buffer[w] = static_cast<unsigned char*>(buffers[w]);
+    *comm = c;
+    return 0;
+}
+
+int FlashLLM_Comm_Destroy(void* comm)
+{
+    delete static_cast<FlashLLMComm*>(comm);
+    return 0;
+}
+
+int FlashLLM_SpMM_SplitK_AllReduce(void*       comm,
+                                   void*       stream,
+                                   const void* Compressed_A,
+                                   const int*  TileOffsets,
+                                   const void* B,
+                                   void*       C,
+                                   int         M,
+                                   int         N,
+                                   int         K,
+                                   const void* bias,
+                                   int         activation,
+                                   int         phases)
+{
+    if (comm == nullptr || (activation != kActNone && activation != kActRelu) || phases < 1 || phases > 3)
+        return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(spmm_launch_all(static_cast<cudaStream_t>(stream), static_cast<const uint4*>(Compressed_A),
+                                            TileOffsets, static_cast<const half*>(B), static_cast<half*>(C), M, N, K,
+                                            nullptr, 1, static_cast<const half*>(bias), activation,
+                                            static_cast<FlashLLMComm*>(comm), phases));
 }
 
 int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K)

@@ -384,6 +384,7 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
         __syncwarp();
         ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     }
+    push_raise_flags(p, *abort_flag == 0u);
     if (warp == mma_warp) {
         __syncwarp();
         ptx::tmem_dealloc(tmem_acc, kTmemCols);

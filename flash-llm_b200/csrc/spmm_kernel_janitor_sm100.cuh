@@ -1,23 +1,23 @@
-// Load-as-Sparse / Compute-as-Dense SpMM for sm_100a, continuous-stream form.
+// Load-as-Sparse / Compute-as-Dense SpMM for sm_100a, register-streaming form with a janitor warp.
 //
 // Same work split as the register-streaming form (one CTA = one 128-row tile row x one N tile x a K range; B loader,
-// two MMA issuers with an accumulator each, scatter warps that also run the epilogue), with three changes that take
-// the per-stage chain "wait for the stage -> clear -> scatter -> publish -> refill" apart:
+// two MMA issuers with an accumulator each, scatter warps that fetch a whole tile into registers with 16-byte global
+// loads and also run the epilogue), with the per-stage chain "wait for the stage -> clear -> scatter -> publish ->
+// refill" taken apart:
 //
-//   * A scatter warp treats the tiles it owns (w, w + WARPS, ...) as ONE stream of 32-vector rows and keeps CAP rows of
-//     it in registers as a circular window: as soon as a row has been scattered, the register it sat in is refilled
-//     with the row CAP places further down the stream, whichever tile that belongs to.  Global loads are therefore in
-//     flight all the time (CAP x 512 bytes per warp), not only between a publish and the next scatter, and tiles of any
-//     density go through the same path (the reference keeps a whole tile in registers, csrc/SpMM_Kernel.cuh:17-62,
-//     which caps a tile at 4096 non-zeros).
 //   * Stages are cleared by a warp of their own, the janitor: it waits for the commit that hands a stage back, fills
 //     it with zeros (32 16-byte stores per lane) and signals an mbarrier the next scatter warp waits on.  The clear is
-//     thereby off the scatter warps' chain and overlaps their work on other stages.  (Clearing with the TMA unit -- a
+//     off the scatter warps' chain and overlaps their work on other stages, and a scatter warp's loads for its next
+//     tile are in flight while the multiply and the clear of its previous one run.  (Clearing with the TMA unit -- a
 //     tensor copy whose box lies wholly outside its tensor writes the fill value without reading global memory -- was
 //     measured: one 16 KB fill every ~900 cycles per SM however many are in flight, three times too slow.  The
 //     reference clears with zero-size cp.async, csrc/SpMM_Kernel.cuh:114-136.)
-//   * Stages are decoupled from warps (tile j lives in stage j mod a_stages, a_stages >= WARPS): a warp that has
-//     published a tile goes on with its next one in another stage instead of waiting for its own stage to come back.
+//   * Stages are decoupled from warps (tile j lives in stage j mod a_stages, a_stages >= WARPS): with spare stages a
+//     warp that has published a tile goes on with its next one instead of waiting for its own stage to come back.
+//   * Six scatter warps per CTA, two CTAs per SM, is the default shape: a tile's loads are issued as one batch and
+//     consumed as one batch (a window refilled row by row was measured at a third of the speed: the hardware tracks
+//     outstanding loads with a handful of counters per warp, and waiting for an old load then also waits for the young
+//     ones that share its counter), so what keeps the memory system busy is the number of warps with a batch in flight.
 #pragma once
 #include "spmm_kernel_direct_sm100.cuh"
 
@@ -26,7 +26,7 @@ namespace flashllm {
 // Warps of the continuous-stream kernel: B loader, janitor, kDirectIssuers MMA issuers, then the scatter warps.
 template<int N_TILE, int CAP, int WARPS, int MIN_BLOCKS>
 __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
-    spmm_tcgen05_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const SpmmParams p)
+    spmm_tcgen05_janitor_kernel(const __grid_constant__ CUtensorMap tmap_b, const SpmmParams p)
 {
     static_assert(N_TILE == 16 || N_TILE == 32 || N_TILE == 64 || N_TILE == 128, "unsupported MMA N");
     static_assert(WARPS >= 4 && WARPS <= 12, "four warps cover the TMEM lane quarters in the epilogue");
@@ -35,6 +35,11 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     constexpr uint32_t kTmemCols = MI * N_TILE < 32 ? 32 : MI * N_TILE;  // a power of two for MI = 2
     constexpr int      NSW       = WARPS;
 
+#ifdef FLASHLLM_TRACE
+    __shared__ unsigned int s_trace[kTraceKinds * kTraceDepth];
+    for (int i = threadIdx.x; i < kTraceKinds * kTraceDepth; i += blockDim.x)
+        s_trace[i] = 0;
+#endif
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base     = (raw_addr + 1023u) & ~1023u;  // swizzled operands need 1024-byte alignment
@@ -93,7 +98,11 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     // ---- set-up
     if (threadIdx.x == 0) {
         for (int i = 0; i < a_stages; ++i) {
+#ifdef FLASHLLM_LANE_ARRIVE
+            ptx::mbar_init(a_full + 8u * i, 32);  // every lane of the scatter warp arrives for itself
+#else
             ptx::mbar_init(a_full + 8u * i, 1);
+#endif
             ptx::mbar_init(a_empty + 8u * i, 1);
             ptx::mbar_init(a_zero + 8u * i, 1);
         }
@@ -142,10 +151,17 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     }
     else if (warp == z_warp) {
         // ================================================================ janitor: clears stages that were handed back
+#ifdef FLASHLLM_SELF_CLEAR
+        if (false) {
+#else
         if (L > 0 && go) {
+#endif
             const int first = L < a_stages ? L : a_stages;
             for (int s = 0; s < first; ++s) {  // every stage starts out cleared
                 zero_fill_stage(a_base + s * kDenseTileBytes, lane);
+#ifdef FLASHLLM_JANITOR_FENCE
+                ptx::fence_proxy_async_smem();
+#endif
                 __syncwarp();  // every lane's stores precede lane 0's release
                 if (lane == 0)
                     ptx::mbar_arrive(a_zero + 8u * s);
@@ -153,12 +169,21 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
             int      s   = 0;
             uint32_t par = 0;
             for (int j = 0; j + a_stages < L; ++j) {  // tile j's stage is reused by tile j + a_stages
+                if (lane == 0)
+                    FL_TRACE(14, j);
                 if (!wait_bounded_warp(a_empty + 8u * s, par, abort_flag, p.status))
                     break;
+                if (lane == 0)
+                    FL_TRACE(15, j);
                 zero_fill_stage(a_base + s * kDenseTileBytes, lane);
+#ifdef FLASHLLM_JANITOR_FENCE
+                ptx::fence_proxy_async_smem();
+#endif
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(a_zero + 8u * s);
+                if (lane == 0)
+                    FL_TRACE(16, j);
                 if (++s == a_stages) {
                     s = 0;
                     par ^= 1u;
@@ -181,12 +206,14 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                 uint32_t       a_par = static_cast<uint32_t>(m / a_stages) & 1u, b_par = 0;
                 bool           ready = false, first_in_batch = true;
                 for (int j = m; j < L; j += MI) {
+                    FL_TRACE(7, j);
                     if (!ready) {
                         if (!wait_bounded(a_full + 8u * s, a_par, abort_flag, p.status))
                             break;
                         if (first_in_batch && !wait_bounded(b_full + 8u * bs, b_par, abort_flag, p.status))
                             break;
                     }
+                    FL_TRACE(9, j);
                     int      s_n = s + MI, kb_n = kb + MI, bs_n = bs;
                     uint32_t a_par_n = a_par, b_par_n = b_par;
                     while (s_n >= a_stages) {
@@ -214,6 +241,7 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                         b_desc0 + static_cast<uint32_t>((bs * KB + kb) * (kBSlab >> 4)), idesc, j != m ? 1u : 0u, a_empty + 8u * s,
                         b_empty + 8u * bs, (batch_done || !has_next) ? 1u : 0u, a_full + 8u * s_n, a_par_n, b_full + 8u * bs_n,
                         b_par_n, has_next ? 1u : 0u, (has_next && batch_done) ? 1u : 0u);
+                    FL_TRACE(10, j);
                     first_in_batch = batch_done;
                     s     = s_n;
                     kb    = kb_n;
@@ -229,123 +257,120 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
         // ================================================================ scatter warps
         const int sw = warp - first_sw;
         if (sw < L && go) {
-            uint4 win[CAP];  // the window: rows i, i+1, ... of this warp's stream, row r in win[r mod CAP]
+            uint4 nxt[CAP];  // words of the tile about to be scattered (loads in flight)
 #pragma unroll
             for (int q = 0; q < CAP; ++q)
-                win[q] = make_uint4(0u, 0u, 0u, 0u);
-
-            // ---- load cursor: the next row to request
-            int          lt     = sw;  // its tile (>= L: the stream has ended)
-            int          l_left = 0;   // vectors of that tile not yet requested
-            const uint4* l_src  = p.compressed;
-            auto load_enter_tile = [&]() {  // positions the cursor on the first non-empty tile at or after lt
-                while (lt < L) {
-                    const int vb = offs[lt], ve = offs[lt + 1];
-                    int       n  = ve - vb;
-                    n            = n < 0 ? 0 : (n > kMaxTileVectors ? kMaxTileVectors : n);
-                    if (n > 0) {
-                        l_left = n;
-                        l_src  = p.compressed + vb;
-                        if (lane == 0) {  // pull a later tile of this warp from DRAM into L2 ahead of its register loads
-                            const int t = lt + kPrefetchAhead * NSW;
-                            if (t < L && offs[t + 1] > offs[t])
-                                ptx::prefetch_l2_bulk(p.compressed + offs[t], static_cast<uint32_t>(offs[t + 1] - offs[t]) * 16u);
-                        }
-                        return;
-                    }
-                    lt += NSW;
-                }
-                l_left = 0;
-            };
-            load_enter_tile();
-
-            // ---- scatter cursor: the row about to be written
-            int      st     = sw;               // its tile
-            int      s_idx  = sw % a_stages;    // that tile's stage ...
-            uint32_t s_par  = static_cast<uint32_t>(sw / a_stages) & 1u;  // ... and which use of it
-            int      s_left = 0;                // vectors of that tile not yet scattered
-            bool     ok     = true;
-
-            // prologue: the first CAP rows of the stream
-#pragma unroll
-            for (int q = 0; q < CAP; ++q) {
-                if (lt < L) {
-                    if (lane < l_left)
-                        win[q] = ldg_stream16(l_src + lane);
-                    l_src += 32;
-                    l_left -= 32;
-                    if (l_left <= 0) {
-                        lt += NSW;
-                        load_enter_tile();
-                    }
-                }
-            }
-
-            // Enters tile st: waits until its stage holds zeros; tiles without words are published at once.
-            auto scatter_enter_tile = [&]() {
-                while (st < L) {
-                    ok = wait_bounded_warp(a_zero + 8u * s_idx, s_par, abort_flag, p.status);
-                    if (!ok)
-                        return;
-                    int n = offs[st + 1] - offs[st];
-                    n     = n < 0 ? 0 : (n > kMaxTileVectors ? kMaxTileVectors : n);
-                    if (n > 0) {
-                        s_left = n;
-                        return;
-                    }
-#ifndef FLASHLLM_CONSUMER_FENCE
-                    ptx::fence_proxy_async_smem();  // the janitor's zeros, observed through a_zero, reach the tensor core
-#endif
-                    if (lane == 0)
-                        ptx::mbar_arrive(a_full + 8u * s_idx);  // an all-zero tile
-                    st += NSW;
-                    s_idx += NSW;
-                    while (s_idx >= a_stages) {
-                        s_idx -= a_stages;
-                        s_par ^= 1u;
-                    }
-                }
-            };
-            scatter_enter_tile();
-
-            while (ok && st < L) {
+                nxt[q] = make_uint4(0u, 0u, 0u, 0u);
+            int          n_in = 0;  // vectors of the tile in nxt
+            const uint4* src  = p.compressed;
+            // Requests the first CAP rows (32 vectors each) of a tile as one batch; rows past the tile's end are
+            // skipped by real branches, not issued predicated off.
+            auto fetch = [&](int vb, int ve, int t) {
+                int n = ve - vb;
+                n     = n < 0 ? 0 : (n > kMaxTileVectors ? kMaxTileVectors : n);  // the slice was validated at set-up
+                n_in  = n;
+                src   = p.compressed + vb;
 #pragma unroll
                 for (int q = 0; q < CAP; ++q) {
-                    if (!(ok && st < L))
+                    if (q * 32 >= n)
                         break;
-                    const uint32_t stage = a_base + static_cast<uint32_t>(s_idx) * kDenseTileBytes;
-                    if (lane < s_left)
-                        scatter_vector(stage, win[q]);
-                    s_left -= 32;
-                    const bool tile_done = s_left <= 0;
-                    if (tile_done) {
-#ifndef FLASHLLM_CONSUMER_FENCE
-                        ptx::fence_proxy_async_smem();  // generic-proxy stores -> the tensor core's async-proxy reads
+                    if (q * 32 + lane < n)
+                        nxt[q] = ldg_stream16(src + q * 32 + lane);
+                }
+                // ... and a later tile of this warp is pulled from DRAM into L2, so that its register loads, issued
+                // a tile or two from now, only have the L2 latency left to hide
+                if (lane == 0) {
+                    const int a = t + kPrefetchAhead * NSW;
+                    if (a < L && offs[a + 1] > offs[a])
+                        ptx::prefetch_l2_bulk(p.compressed + offs[a], static_cast<uint32_t>(offs[a + 1] - offs[a]) * 16u);
+                }
+            };
+            fetch(offs[sw], offs[sw + 1], sw);
+            if (lane == 0 && sw + NSW < L && offs[sw + NSW + 1] > offs[sw + NSW])
+                ptx::prefetch_l2_bulk(p.compressed + offs[sw + NSW],
+                                      static_cast<uint32_t>(offs[sw + NSW + 1] - offs[sw + NSW]) * 16u);
+
+            int      s_idx = sw % a_stages;                                // stage of tile j ...
+            uint32_t s_par = static_cast<uint32_t>(sw / a_stages) & 1u;    // ... and which use of it
+            for (int j = sw; j < L; j += NSW) {
+                // Offsets of this warp's following tile, read before the proxy fence below: a shared-memory load
+                // issued behind that fence waits for it.
+                const bool has_next = j + NSW < L;
+                int        vb2 = 0, ve2 = 0;
+                if (has_next) {
+                    vb2 = offs[j + NSW];
+                    ve2 = offs[j + NSW + 1];
+                }
+                if (lane == 0)
+                    FL_TRACE(0, j);
+                const uint32_t stage = a_base + static_cast<uint32_t>(s_idx) * kDenseTileBytes;
+#ifdef FLASHLLM_SELF_CLEAR
+                if (j >= a_stages && !wait_bounded_warp(a_empty + 8u * s_idx, s_par ^ 1u, abort_flag, p.status))
+                    break;
+                zero_fill_stage(stage, lane);
+                __syncwarp();
+#else
+                if (!wait_bounded_warp(a_zero + 8u * s_idx, s_par, abort_flag, p.status))
+                    break;
 #endif
-                        __syncwarp();  // every lane's stores precede lane 0's release
-                        if (lane == 0)
-                            ptx::mbar_arrive(a_full + 8u * s_idx);
+                if (lane == 0)
+                    FL_TRACE(3, j);
+                const int      n_reg = n_in < CAP * 32 ? n_in : CAP * 32;
+#pragma unroll
+                for (int q = 0; q < CAP; ++q) {
+                    if (q * 32 >= n_reg)
+                        break;
+                    if (q * 32 + lane < n_reg)
+                        scatter_vector(stage, nxt[q]);
+                }
+                // tiles denser than the register budget: the rest in further batches, fetched only now
+                for (int v0 = n_reg; v0 < n_in; v0 += CAP * 32) {
+#pragma unroll
+                    for (int q = 0; q < CAP; ++q) {
+                        if (v0 + q * 32 >= n_in)
+                            break;
+                        if (v0 + q * 32 + lane < n_in)
+                            nxt[q] = ldg_stream16(src + v0 + q * 32 + lane);
                     }
-                    // the register is free again: request the row CAP places further down the stream
-                    if (lt < L) {
-                        if (lane < l_left)
-                            win[q] = ldg_stream16(l_src + lane);
-                        l_src += 32;
-                        l_left -= 32;
-                        if (l_left <= 0) {
-                            lt += NSW;
-                            load_enter_tile();
-                        }
+#pragma unroll
+                    for (int q = 0; q < CAP; ++q) {
+                        if (v0 + q * 32 >= n_in)
+                            break;
+                        if (v0 + q * 32 + lane < n_in)
+                            scatter_vector(stage, nxt[q]);
                     }
-                    if (tile_done) {
-                        st += NSW;
-                        s_idx += NSW;
-                        while (s_idx >= a_stages) {
-                            s_idx -= a_stages;
-                            s_par ^= 1u;
-                        }
-                        scatter_enter_tile();
-                    }
+                }
+                if (lane == 0)
+                    FL_TRACE(5, j);
+#ifdef FLASHLLM_FETCH_FIRST
+                if (has_next)
+                    fetch(vb2, ve2, j + NSW);
+#endif
+#ifndef FLASHLLM_CONSUMER_FENCE
+                ptx::fence_proxy_async_smem();  // generic-proxy stores (the janitor's zeros, observed through a_zero,
+                                                // and this warp's words) -> the tensor core's async-proxy reads
+#endif
+                if (lane == 0)
+                    FL_TRACE(17, j);
+#ifdef FLASHLLM_LANE_ARRIVE
+                ptx::mbar_arrive(a_full + 8u * s_idx);
+#else
+                __syncwarp();  // every lane's stores precede lane 0's release
+                if (lane == 0)
+                    FL_TRACE(18, j);
+                if (lane == 0)
+                    ptx::mbar_arrive(a_full + 8u * s_idx);
+#endif
+                if (lane == 0)
+                    FL_TRACE(6, j);
+#ifndef FLASHLLM_FETCH_FIRST
+                if (has_next)
+                    fetch(vb2, ve2, j + NSW);
+#endif
+                s_idx += NSW;
+                while (s_idx >= a_stages) {
+                    s_idx -= a_stages;
+                    s_par ^= 1u;
                 }
             }
         }
@@ -373,10 +398,16 @@ __global__ void __launch_bounds__((2 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
         __syncwarp();
         ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     }
+    push_raise_flags(p, *abort_flag == 0u);
     if (warp == mma_warp) {
         __syncwarp();
         ptx::tmem_dealloc(tmem_acc, kTmemCols);
     }
+#ifdef FLASHLLM_TRACE
+    if (blockIdx.y == FLASHLLM_TRACE && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < kTraceKinds * kTraceDepth; i += blockDim.x)
+            g_trace[i] = s_trace[i];
+#endif
 }
 
 }  // namespace flashllm

@@ -30,6 +30,8 @@
 
 namespace flashllm {
 
+constexpr int kMaxPushWorld = 8;  // GPUs of one NVSwitch box (fused all-reduce)
+
 struct SpmmParams {
     const uint4*  compressed;    // tiled-CSL words viewed as 16-byte vectors
     const int*    tile_offsets;  // T + 2 prefix sums, in vectors
@@ -41,6 +43,13 @@ struct SpmmParams {
     int           M, N, K;
     int           k_tiles;  // K / 64
     SpmmPlan      plan;
+    // Fused all-reduce of a row-parallel SpMM (push_world > 0): every finished fp32 value of this GPU's partial product
+    // is stored into the receive slot this rank owns on every GPU of the group (its own included) instead of C, and
+    // each CTA then raises one flag per GPU; allreduce_sum_kernel on each GPU adds the slots up.
+    int           push_world;
+    unsigned int  push_epoch;                  // value the flags are raised to by this call
+    float*        push_slot[kMaxPushWorld];    // [N][M] fp32 slot of this rank in GPU w's receive buffer
+    unsigned int* push_flag[kMaxPushWorld];    // this rank's flags in GPU w's receive buffer, one per CTA of the grid
 };
 
 constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
@@ -296,7 +305,11 @@ __device__ __forceinline__ void accumulators_to_output(const SpmmParams& p, uint
                 for (int i = 0; i < 8; ++i)
                     if (c0 + i < n_valid) {
                         const size_t at = static_cast<size_t>(c0 + i) * p.M + row_in_tile;
-                        if (part_tile)
+                        if (p.push_world > 0) {
+                            for (int w = 0; w < p.push_world; ++w)
+                                p.push_slot[w][tile_off + at] = r[i];
+                        }
+                        else if (part_tile)
                             part_tile[at] = r[i];
                         else
                             out_tile[at] = finish_output(r[i], p.bias, tile_row * kTileM + row_in_tile, p.activation);
@@ -332,11 +345,31 @@ __device__ __forceinline__ void cluster_reduce_store(const SpmmParams& p, uint32
         for (int q = 0; q < S; ++q)
             acc += ptx::ld_dsmem_f32(ptx::map_to_rank(base + static_cast<uint32_t>(e) * 4u, q));
         if (store_ok) {
-            if (part_tile)
+            if (p.push_world > 0) {
+                for (int w = 0; w < p.push_world; ++w)
+                    p.push_slot[w][tile_off + static_cast<size_t>(n) * p.M + m] = acc;
+            }
+            else if (part_tile)
                 part_tile[static_cast<size_t>(n) * p.M + m] = acc;
             else
                 out_tile[static_cast<size_t>(n) * p.M + m] = finish_output(acc, p.bias, tile_row * kTileM + m, p.activation);
         }
+    }
+}
+
+// Fused all-reduce, sending side: called by every thread of a CTA after its last store of partial sums.  The barrier
+// orders the CTA's stores before thread 0's system-scope fence, after which the flag of this CTA is raised on every GPU
+// of the group.  Plain peer stores only.
+__device__ __forceinline__ void push_raise_flags(const SpmmParams& p, bool cta_ok)
+{
+    if (p.push_world <= 0)
+        return;
+    __syncthreads();
+    if (threadIdx.x == 0 && cta_ok) {  // a CTA that gave up raises nothing: the receivers' waits run out and say so
+        __threadfence_system();
+        const unsigned int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        for (int w = 0; w < p.push_world; ++w)
+            *reinterpret_cast<volatile unsigned int*>(p.push_flag[w] + cta) = p.push_epoch;
     }
 }
 
@@ -805,6 +838,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         __syncwarp();
         ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     }
+    push_raise_flags(p, *abort_flag == 0u);
     if (warp == mma_warp) {
         __syncwarp();
         ptx::tmem_dealloc(tmem_acc, kTmemCols);
@@ -871,6 +905,76 @@ __global__ void splitk_reduce_kernel(half* __restrict__ C, const half* __restric
     for (int i = 0; i < 4; ++i)
         oh[i] = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
     *reinterpret_cast<uint4*>(C + i8) = o;
+}
+
+constexpr unsigned kStatusPeerWaitExpired = 32u;  // a GPU of the group did not deliver its partial sums in time
+
+// Fused all-reduce, receiving side: C = fp16(act(sum over the group's GPUs of their fp32 partial products + bias)).
+// `slots` holds `world` matrices [N][M] fp32, `slot_stride` floats apart (slot w written by GPU w); `flags` holds, for
+// each sender, `flag_stride` words of which the first `flags_per_rank` are in use (one per CTA of the sending grid).
+// Before a CTA reads anything it waits, bounded, until every flag of every sender has reached `epoch` (a sender raises
+// a flag after the stores of one CTA, so all of them together cover the whole matrix).  Slots are added in rank order
+// on every GPU, so all GPUs get the same bits.
+__global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, long long slot_stride,
+                                     const unsigned int* flags, int flag_stride, unsigned int epoch, int world,
+                                     int flags_per_rank, long long count, const half* __restrict__ bias, int M,
+                                     int activation, unsigned int* status)
+{
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    __shared__ int s_ok;
+    if (threadIdx.x == 0)
+        s_ok = 1;
+    __syncthreads();
+    const int total_flags = world * flags_per_rank;
+    bool      mine_ok     = true;
+    uint64_t  t0          = 0;
+    for (int f = threadIdx.x; f < total_flags && mine_ok; f += blockDim.x) {
+        const volatile unsigned int* flag = flags + static_cast<long long>(f / flags_per_rank) * flag_stride + f % flags_per_rank;
+        for (uint32_t it = 1;; ++it) {
+            // flags only ever grow (one step per call): "reached" = not behind, also across the 32-bit wrap
+            if (static_cast<int>(*flag - epoch) >= 0)
+                break;
+            __nanosleep(100);
+            if ((it & 255u) == 0u) {
+                const uint64_t now = ptx::globaltimer_ns();
+                if (t0 == 0)
+                    t0 = now;
+                else if (now - t0 > kWaitLimitNs) {
+                    mine_ok = false;
+                    break;
+                }
+            }
+        }
+    }
+    if (!mine_ok)
+        s_ok = 0;
+    __threadfence_system();  // the flags were observed: the peers' stores before them are visible to the loads below
+    __syncthreads();
+    if (!s_ok) {
+        if (threadIdx.x == 0)
+            atomicOr(status, kStatusPeerWaitExpired);
+        return;  // nothing is stored: the caller reads the status word
+    }
+    const long long i4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i4 >= count)
+        return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int w = 0; w < world; ++w) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(slots + static_cast<long long>(w) * slot_stride + i4));
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+    }
+    const int m = static_cast<int>(i4 % M);
+    uint2     o;
+    half*     oh = reinterpret_cast<half*>(&o);
+    oh[0]        = finish_output(acc.x, bias, m, activation);
+    oh[1]        = finish_output(acc.y, bias, m + 1, activation);
+    oh[2]        = finish_output(acc.z, bias, m + 2, activation);
+    oh[3]        = finish_output(acc.w, bias, m + 3, activation);
+    *reinterpret_cast<uint2*>(C + i4) = o;
 }
 
 }  // namespace flashllm

@@ -62,16 +62,21 @@ def shard_weights(shape: ChainShape, rank: int, w_qkv: torch.Tensor, w_out: torc
 
 
 def run_chain(shape: ChainShape, x: torch.Tensor, matmul: Callable[..., torch.Tensor],
-              all_reduce: Callable[[torch.Tensor], torch.Tensor]) -> torch.Tensor:
+              all_reduce: Callable[[torch.Tensor], torch.Tensor] | None = None,
+              matmul_reduced: Callable[[str, torch.Tensor], torch.Tensor] | None = None) -> torch.Tensor:
     """One rank's pass over the layer.  `matmul(name, X[N][K], relu=False) -> Y[N][M]` multiplies by that rank's shard
-    `name` (and applies ReLU to the result when asked: FFN1 is column-parallel, so its activation needs no partner);
-    `all_reduce(t)` returns the sum of `t` over the ranks.  Returns the layer output [N][H] (same on every rank)."""
+    `name` (and applies ReLU to the result when asked: FFN1 is column-parallel, so its activation needs no partner).
+    The two row-parallel layers need the sum over the ranks: either `all_reduce(t)` is applied to their outputs, or
+    `matmul_reduced(name, X)` does the matmul and the sum in one step (the fused SpMM + all-reduce of the library).
+    Returns the layer output [N][H] (same on every rank)."""
+    if matmul_reduced is None:
+        matmul_reduced = lambda name, t: all_reduce(matmul(name, t))  # noqa: E731
     h = shape.hidden // shape.world
     y_qkv = matmul("qkv", x)                               # [N][3H/g]: this rank's Q, K, V features
     v = y_qkv[:, 2 * h:3 * h].contiguous()                 # single-position attention returns V
-    attn = all_reduce(matmul("out_proj", v))               # [N][H], partial sums over the K slices
+    attn = matmul_reduced("out_proj", v)                   # [N][H], partial sums over the K slices added up
     y1 = matmul("ffn1", attn, relu=True)                   # [N][F/g]
-    return all_reduce(matmul("ffn2", y1))                  # [N][H]
+    return matmul_reduced("ffn2", y1)                      # [N][H]
 
 
 def fp32_all_reduce(dist=None) -> Callable[[torch.Tensor], torch.Tensor]:
@@ -133,5 +138,60 @@ class DeviceChain:
                                      self.fl.ACT_RELU if relu else self.fl.ACT_NONE)
         return layer["out"]
 
-    def step(self, x: torch.Tensor, all_reduce: Callable[[torch.Tensor], torch.Tensor]) -> torch.Tensor:
+    def matmul_reduced(self, comm) -> Callable[[str, torch.Tensor], torch.Tensor]:
+        """The row-parallel layers through the library's fused SpMM + all-reduce over the communicator `comm`."""
+        def call(name: str, x: torch.Tensor) -> torch.Tensor:
+            layer = self.layers[name]
+            assert x.is_contiguous() and x.dtype == torch.float16 and tuple(x.shape) == (self.shape.tokens, layer["K"])
+            stream = torch.cuda.current_stream(self.dev).cuda_stream
+            self.fl.spmm_splitk_allreduce(comm, stream, layer["comp"].data_ptr(), layer["offs"].data_ptr(), x.data_ptr(),
+                                          layer["out"].data_ptr(), layer["M"], self.shape.tokens, layer["K"])
+            return layer["out"]
+        return call
+
+    def step(self, x: torch.Tensor, all_reduce: Callable[[torch.Tensor], torch.Tensor] | None = None,
+             comm=None) -> torch.Tensor:
+        """One pass; with `comm` (see PeerGroup) the row-parallel layers use the fused SpMM + all-reduce."""
+        if comm is not None:
+            return run_chain(self.shape, x, self.matmul, matmul_reduced=self.matmul_reduced(comm))
         return run_chain(self.shape, x, self.matmul, all_reduce)
+
+
+class PeerGroup:
+    """This rank's communicator for the fused SpMM + all-reduce: allocates the local receive buffer, exchanges the
+    inter-process handles over `dist` (any torch.distributed backend: the handles are 64 bytes of host data), maps the
+    peers' buffers and builds the communicator.  `max_elems` = the largest M*N of a fused call."""
+
+    def __init__(self, fl, dist, rank: int, world: int, max_elems: int):
+        self.fl, self.rank, self.world = fl, rank, world
+        self.local, handle = fl.comm_alloc_buffer(world, max_elems)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        self.buffers = [self.local if w == rank else fl.comm_open_peer_buffer(handles[w]) for w in range(world)]
+        self.comm = fl.comm_create(rank, world, max_elems, self.buffers)
+        dist.barrier()  # every buffer is cleared and mapped before anybody's first store into it
+
+    def close(self):
+        self.fl.comm_destroy(self.comm)
+        for w, ptr in enumerate(self.buffers):
+            if w != self.rank:
+                self.fl.comm_close_peer_buffer(ptr)
+        self.fl.comm_free_buffer(self.local)
+
+
+class LocalGroup:
+    """`world` communicators on ONE device, for tests without several GPUs: the ranks' receive buffers all live on
+    this device.  The fused call never waits inside its first kernel, so the ranks' calls can be enqueued one after
+    another on one stream: every "rank"'s stores have landed by the time any summing kernel runs ... provided that all
+    ranks' first kernels are enqueued before any rank's second one, which is what `calls()` arranges."""
+
+    def __init__(self, fl, world: int, max_elems: int):
+        self.fl, self.world = fl, world
+        self.buffers = [fl.comm_alloc_buffer(world, max_elems)[0] for _ in range(world)]
+        self.comms = [fl.comm_create(r, world, max_elems, self.buffers) for r in range(world)]
+
+    def close(self):
+        for c in self.comms:
+            self.fl.comm_destroy(c)
+        for b in self.buffers:
+            self.fl.comm_free_buffer(b)
