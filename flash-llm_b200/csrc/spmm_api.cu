@@ -60,9 +60,17 @@ static std::once_flag g_encode_once;
 // i.e. 62.5 % sparsity, need no overflow loop), for its two shapes: 8 scatter warps and one CTA per SM; 4 scatter
 // warps and two CTAs per SM.
 #ifndef FLASHLLM_NARROW_CAP
-#define FLASHLLM_NARROW_CAP 16
+#define FLASHLLM_NARROW_CAP 14
 #endif
-constexpr int kDirectCapWide = 24, kDirectCapNarrow = FLASHLLM_NARROW_CAP;
+#ifndef FLASHLLM_PAIR_CAP
+#define FLASHLLM_PAIR_CAP 8
+#endif
+// ... and of its shape with two warps per tile (4 stages, 8 scatter warps, two CTAs per SM): rows per warp
+#ifndef FLASHLLM_DIRECT_BLOCKS
+#define FLASHLLM_DIRECT_BLOCKS 2
+#endif
+constexpr int kDirectBlocks = FLASHLLM_DIRECT_BLOCKS;  // CTAs per SM of the 4-stage shapes
+constexpr int kDirectCapWide = 24, kDirectCapNarrow = FLASHLLM_NARROW_CAP, kDirectCapPair = FLASHLLM_PAIR_CAP;
 
 // Rows (32 vectors each) of the continuous-stream kernel's register window, for its three shapes: 4 or 6 scatter
 // warps with two CTAs per SM, 8 scatter warps with one CTA per SM.
@@ -96,7 +104,9 @@ static cudaError_t raise_smem_limit(int optin)
     if (e == cudaSuccess)
         e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapWide, 8, 1>, optin);
     if (e == cudaSuccess)
-        e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, 2>, optin);
+        e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, kDirectBlocks>, optin);
+    if (e == cudaSuccess)
+        e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapPair, 4, 2, 2>, optin);
     if (e == cudaSuccess)
         e = raise_smem_limit_of(spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap4, 4, 2>, optin);
     if (e == cudaSuccess)
@@ -236,7 +246,8 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
         if (!ov.v[kPlanBBatch])
             pl.b_batch = (pl.b_batch + kDirectIssuers - 1) / kDirectIssuers * kDirectIssuers;
         pl.a_stages      = pl.scatter_warps;
-        pl.producers     = 0;
+        // `producers` of the register-streaming form = warps that share one tile (1, or 2 with four stages)
+        pl.producers     = (!janitor && ov.v[kPlanProducers] == 2 && pl.scatter_warps == 4) ? 2 : (janitor ? 0 : 1);
         pl.ring_slots    = 0;
         pl.chunk_vectors = 0;
     }
@@ -250,7 +261,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // distributed shared memory, CTAs co-scheduled) except on small problems, where the second launch costs more
     // than it saves; clusters also take what the workspace cannot.  Replaces the reference's hand-tuned Split_K
     // tables (kernel_benchmark/benchmark.sh:13-15).
-    const int slots     = st->sm_count * (two_per_sm ? 2 : 1);
+    const int slots     = st->sm_count * (two_per_sm ? ((direct && !janitor && pl.producers == 1) ? kDirectBlocks : 2) : 1);
     const int max_extra = ((static_cast<long long>(M) * N) % 4 != 0) ? 1 : (Split_K / 2 > 1 ? Split_K / 2 : 1);
     // (with launch overlap on, the second kernel hides behind its neighbours and workspace parts win at every size)
     const bool small    = static_cast<long long>(tile_rows) * k_tiles <= 4096
@@ -350,7 +361,7 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cudaLaunchAttribute attr[2];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
     cfg.blockDim         = dim3((pl.path == kPathJanitor   ? 2 + kDirectIssuers + pl.scatter_warps
-                                 : pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps
+                                 : pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps * pl.producers
                                                           : pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream           = stream;
@@ -376,7 +387,9 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     if (pl.path == kPathDirect) {
         if (pl.scatter_warps == 8)
             return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapWide, 8, 1>, tmap, params);
-        return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, 2>, tmap, params);
+        if (pl.producers == 2)
+            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapPair, 4, 2, 2>, tmap, params);
+        return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, kDirectBlocks>, tmap, params);
     }
     return cudaLaunchKernelEx(&cfg, spmm_tcgen05_kernel<N_TILE>, tmap, params);
 }

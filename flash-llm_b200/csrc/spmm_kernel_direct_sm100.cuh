@@ -28,6 +28,81 @@ __device__ __forceinline__ uint4 ldg_stream16(const uint4* ptr)
     return v;
 }
 
+// Straight-line forms for the scatter warps' per-tile path.  That path is bound by the number of instructions and
+// branches a warp has to get through per tile, so a row of 32 vectors is loaded / scattered by predicated instructions
+// behind ONE comparison (`rem` = vectors of the tile from this lane's first one on, against the row's constant offset)
+// instead of being guarded by branches, and row addresses are one base register plus a constant.
+template<int VEC_OFFSET>
+__device__ __forceinline__ void ldg_row_if(uint4& v, const uint4* lane_base, int rem)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.gt.s32 p, %5, %6;\n"
+        "@p " FLASHLLM_LDG_FLAVOUR " {%0, %1, %2, %3}, [%4 + %7];\n"
+        "}\n"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "l"(lane_base), "r"(rem), "n"(VEC_OFFSET), "n"(VEC_OFFSET * 16));
+}
+
+template<int VEC_OFFSET>
+__device__ __forceinline__ void scatter_row_if(uint32_t stage, const uint4& w, int rem)
+{
+    const uint32_t a0 = stage + ((w.x >> 15) & 0x3FFEu), a1 = stage + ((w.y >> 15) & 0x3FFEu);
+    const uint32_t a2 = stage + ((w.z >> 15) & 0x3FFEu), a3 = stage + ((w.w >> 15) & 0x3FFEu);
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.gt.s32 p, %8, %9;\n"
+        "@p st.shared.u16 [%0], %4;\n"
+        "@p st.shared.u16 [%1], %5;\n"
+        "@p st.shared.u16 [%2], %6;\n"
+        "@p st.shared.u16 [%3], %7;\n"
+        "}\n" ::"r"(a0),
+        "r"(a1), "r"(a2), "r"(a3), "h"(static_cast<unsigned short>(w.x & 0xFFFFu)),
+        "h"(static_cast<unsigned short>(w.y & 0xFFFFu)), "h"(static_cast<unsigned short>(w.z & 0xFFFFu)),
+        "h"(static_cast<unsigned short>(w.w & 0xFFFFu)), "r"(rem), "n"(VEC_OFFSET)
+        : "memory");
+}
+
+// Rows [FIRST, LAST) of a warp's share of a tile: the warp's row q is the tile's row q * WPT + its index among the
+// WPT warps that share the tile (already folded into lane_base and rem).
+template<int FIRST, int LAST, int WPT, int CAP>
+__device__ __forceinline__ void load_rows(uint4 (&buf)[CAP], const uint4* lane_base, int rem)
+{
+    if constexpr (FIRST < LAST) {
+        ldg_row_if<FIRST * WPT * 32>(buf[FIRST], lane_base, rem);
+        load_rows<FIRST + 1, LAST, WPT, CAP>(buf, lane_base, rem);
+    }
+}
+
+template<int FIRST, int LAST, int WPT, int CAP>
+__device__ __forceinline__ void scatter_rows(uint32_t stage, const uint4 (&buf)[CAP], int rem)
+{
+    if constexpr (FIRST < LAST) {
+        scatter_row_if<FIRST * WPT * 32>(stage, buf[FIRST], rem);
+        scatter_rows<FIRST + 1, LAST, WPT, CAP>(stage, buf, rem);
+    }
+}
+
+// A warp's batch of up to CAP rows: the lower half always, the upper half only when the tile reaches it (one branch),
+// so that sparse tiles do not pay for rows they do not have.
+template<int WPT, int CAP>
+__device__ __forceinline__ void load_batch(uint4 (&buf)[CAP], const uint4* lane_base, int rem_uniform, int rem)
+{
+    load_rows<0, CAP / 2, WPT, CAP>(buf, lane_base, rem);
+    if (rem_uniform > (CAP / 2) * WPT * 32)
+        load_rows<CAP / 2, CAP, WPT, CAP>(buf, lane_base, rem);
+}
+
+template<int WPT, int CAP>
+__device__ __forceinline__ void scatter_batch(uint32_t stage, const uint4 (&buf)[CAP], int rem_uniform, int rem)
+{
+    scatter_rows<0, CAP / 2, WPT, CAP>(stage, buf, rem);
+    if (rem_uniform > (CAP / 2) * WPT * 32)
+        scatter_rows<CAP / 2, CAP, WPT, CAP>(stage, buf, rem);
+}
+
 // How many of its own tiles ahead a scatter warp asks the memory system to bring into L2 (its register loads run one
 // tile ahead).
 #ifndef FLASHLLM_PREFETCH_AHEAD
@@ -38,23 +113,27 @@ constexpr int kPrefetchAhead = FLASHLLM_PREFETCH_AHEAD;
 // Warps of the register-streaming kernel: one B loader, kDirectIssuers MMA issuers, then the scatter warps.
 constexpr int kDirectIssuers = 2;
 
-// CAP: vectors per lane kept in registers (a tile of up to 32*CAP vectors is handled without the overflow loop).
-// WARPS: scatter warps = stages.  MIN_BLOCKS: CTAs per SM the register budget is sized for.
+// CAP: vectors per lane kept in registers.  WARPS: stages = tiles in flight per CTA.  WPT: warps that share one tile
+// (row q of warp h is the tile's row q * WPT + h), so a tile of up to 32 * CAP * WPT vectors is handled without the
+// overflow loop and a warp's instruction stream per tile is 1 / WPT as long.  MIN_BLOCKS: CTAs per SM the register
+// budget is sized for.
 //
 // One thread cannot issue tcgen05.mma as fast as the tensor core retires them (measured: 4 MMAs and the commit that
 // hands a stage back cost an issuing thread ~400 cycles, the tensor core ~180), so tiles alternate between
 // kDirectIssuers issuing threads, each with an accumulator of its own in tensor memory; the epilogue adds them.
-template<int N_TILE, int CAP, int WARPS, int MIN_BLOCKS>
-__global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
+template<int N_TILE, int CAP, int WARPS, int MIN_BLOCKS, int WPT = 1>
+__global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_BLOCKS)
     spmm_tcgen05_direct_kernel(const __grid_constant__ CUtensorMap tmap_b, const SpmmParams p)
 {
     static_assert(N_TILE == 16 || N_TILE == 32 || N_TILE == 64 || N_TILE == 128, "unsupported MMA N");
     static_assert(WARPS >= 4 && WARPS <= 12, "four warps cover the TMEM lane quarters in the epilogue");
+    static_assert(WPT == 1 || WPT == 2, "a tile is decompressed by one warp or by a pair");
+    static_assert(CAP % 2 == 0 && 32 % WPT == 0, "batches are issued in two halves; the clear is split evenly");
     constexpr uint32_t kBSlab    = N_TILE * kTileK * 2;  // one K tile of B in shared memory
     constexpr int      MI        = kDirectIssuers;
     static_assert(WARPS % MI == 0, "every issuer serves the same stages on every lap");
     constexpr uint32_t kTmemCols = MI * N_TILE < 32 ? 32 : MI * N_TILE;  // a power of two for MI = 2
-    constexpr int      NSW       = WARPS;
+    constexpr int      NSW       = WARPS * WPT;  // scatter warps
     constexpr int      a_stages  = WARPS;
 
 #ifdef FLASHLLM_TRACE
@@ -117,7 +196,7 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
     // ---- set-up
     if (threadIdx.x == 0) {
         for (int i = 0; i < a_stages; ++i) {
-            ptx::mbar_init(a_full + 8u * i, 1);
+            ptx::mbar_init(a_full + 8u * i, WPT);  // every warp that shares the tile publishes its part
             ptx::mbar_init(a_empty + 8u * i, 1);
         }
         for (int i = 0; i < b_stages; ++i) {
@@ -230,51 +309,48 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
         }
     }
     else {
-        // ================================================================ scatter warps: one stage each
+        // ================================================================ scatter warps: WPT warps per stage
         const int sw = warp - first_sw;
+        const int st = sw % WARPS;  // the stage, and the tile stream st, st + WARPS, ... this warp works on
+        const int h  = sw / WARPS;  // its index among the WPT warps that share those tiles
         if (L > 0 && go) {
-            const uint32_t stage     = a_base + sw * kDenseTileBytes;
-            const uint32_t full_bar  = a_full + 8u * sw;
-            const uint32_t empty_bar = a_empty + 8u * sw;
-            uint4          nxt[CAP];  // words of the tile about to be scattered (loads in flight)
+            const uint32_t stage     = a_base + st * kDenseTileBytes;
+            const uint32_t full_bar  = a_full + 8u * st;
+            const uint32_t empty_bar = a_empty + 8u * st;
+            const int      first_vec = h * 32 + lane;  // this lane's vector in row 0 of the warp's share
+            uint4          nxt[CAP];                   // words of the tile about to be scattered (loads in flight)
 #pragma unroll
             for (int q = 0; q < CAP; ++q)
                 nxt[q] = make_uint4(0u, 0u, 0u, 0u);
 
-            int          n_in = 0;  // vectors of the tile in nxt
+            int          n_in = 0;  // vectors of the whole tile whose share is in nxt
             const uint4* src  = p.compressed;
             bool         bad  = false;
             // ---- first tile of this warp
-            if (sw < L) {
-                const int vb = offs[sw], ve = offs[sw + 1];
+            if (st < L) {
+                const int vb = offs[st], ve = offs[st + 1];
                 bad          = (ve < vb) || (ve - vb > kMaxTileVectors) || (vb < 0);
                 n_in         = bad ? 0 : ve - vb;
                 src          = p.compressed + (bad ? 0 : vb);
-#pragma unroll
-                for (int q = 0; q < CAP; ++q) {
-                    if (q * 32 >= n_in)
-                        break;  // a real branch: blocks past the tile's end are skipped, not issued predicated off
-                    if (q * 32 + lane < n_in)
-                        nxt[q] = ldg_stream16(src + q * 32 + lane);
-                }
-                if (lane == 0) {
+                load_batch<WPT, CAP>(nxt, src + first_vec, n_in, n_in - first_vec);
+                if (lane == 0 && h == 0) {
                     for (int a = 1; a < kPrefetchAhead; ++a) {
-                        const int t = sw + a * NSW;
+                        const int t = st + a * WARPS;
                         if (t < L && offs[t + 1] > offs[t])
                             ptx::prefetch_l2_bulk(p.compressed + offs[t], static_cast<uint32_t>(offs[t + 1] - offs[t]) * 16u);
                     }
                 }
             }
             uint32_t use = 0;
-            for (int j = sw; j < L; j += NSW, ++use) {
+            for (int j = st; j < L; j += WARPS, ++use) {
                 // Offsets of this warp's following tile, fetched a whole tile ahead of their use: read after the proxy
                 // fence below, they would wait for it, and the loads that need them would wait for them (measured: the
                 // refill then takes ~7000 cycles instead of ~650).
-                const bool has_next = j + NSW < L;
+                const bool has_next = j + WARPS < L;
                 int        vb2 = 0, ve2 = 0;
                 if (has_next) {
-                    vb2 = offs[j + NSW];
-                    ve2 = offs[j + NSW + 1];
+                    vb2 = offs[j + WARPS];
+                    ve2 = offs[j + WARPS + 1];
                 }
                 if (bad)
                     atomicOr(p.status, kStatusBadTileOffsets);
@@ -283,54 +359,47 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                 bool ok = !bad;
                 if (ok && use > 0)
                     ok = wait_bounded_warp(empty_bar, (use & 1u) ^ 1u, abort_flag, p.status);
-                if (!ok) {  // uniform across the warp
+                if (!ok) {  // uniform across the warps that share the tile: they watch the same barrier and flag
                     if (bad)
                         *abort_flag = 1u;
                     break;
                 }
                 if (lane == 0)
                     FL_TRACE(3, j);
-                // ---- clear the stage, then scatter the new tile
-                if (!(FLASHLLM_ABLATE & 1))
-                    zero_fill_stage(stage, lane);
-                __syncwarp();  // another lane's zero must not land on top of this lane's new value
+                // ---- clear the stage (each sharing warp its part), then scatter the new tile
+                if (!(FLASHLLM_ABLATE & 1)) {
+#pragma unroll
+                    for (int q = 0; q < 32 / WPT; ++q)
+                        sts_zero16(stage + static_cast<uint32_t>((q * WPT + h) * 32 + lane) * 16u);
+                }
+                // another lane's (or the partner warp's) zero must not land on top of a new value
+                if (WPT == 1)
+                    __syncwarp();
+                else
+                    ptx::named_barrier_sync(1u + static_cast<uint32_t>(st), 32u * WPT);
                 if (lane == 0)
                     FL_TRACE(2, j);
-                const int n_reg = n_in < CAP * 32 ? n_in : CAP * 32;
-#pragma unroll
-                for (int q = 0; q < CAP; ++q) {
-                    if (q * 32 >= n_reg)
-                        break;
-                    if (q * 32 + lane < n_reg) {
+                {
+                    const int rem = n_in - first_vec;
 #if (FLASHLLM_ABLATE & 2)
+#pragma unroll
+                    for (int q = 0; q < CAP; ++q)
                         if ((nxt[q].x ^ nxt[q].y ^ nxt[q].z ^ nxt[q].w) == 0x9E3779B9u)  // keeps the loads alive
                             scatter_word(stage, nxt[q].x);
 #else
-                        scatter_vector(stage, nxt[q]);
+                    scatter_batch<WPT, CAP>(stage, nxt, n_in, rem);
 #endif
-                    }
-                }
-
-                // tiles denser than the register budget: the rest in further register loads, fetched only now
-                for (int v0 = n_reg; v0 < n_in; v0 += CAP * 32) {
-#pragma unroll
-                    for (int q = 0; q < CAP; ++q) {
-                        if (v0 + q * 32 >= n_in)
-                            break;
-                        if (v0 + q * 32 + lane < n_in)
-                            nxt[q] = ldg_stream16(src + v0 + q * 32 + lane);
-                    }
-#pragma unroll
-                    for (int q = 0; q < CAP; ++q) {
-                        if (v0 + q * 32 >= n_in)
-                            break;
-                        if (v0 + q * 32 + lane < n_in)
-                            scatter_vector(stage, nxt[q]);
+                    // tiles denser than the register budget: the rest in further batches, fetched only now
+                    for (int v0 = CAP * WPT * 32; v0 < n_in; v0 += CAP * WPT * 32) {
+                        load_batch<WPT, CAP>(nxt, src + v0 + first_vec, n_in - v0, rem - v0);
+                        scatter_batch<WPT, CAP>(stage, nxt, n_in - v0, rem - v0);
                     }
                 }
                 if (lane == 0)
                     FL_TRACE(5, j);
+#if !(FLASHLLM_ABLATE & 16)  // timing only: without the proxy fence the tensor core may read stale words
                 ptx::fence_proxy_async_smem();
+#endif
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(full_bar);
@@ -341,17 +410,12 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS) * 32, MIN_BLOCKS)
                     bad  = (ve2 < vb2) || (ve2 - vb2 > kMaxTileVectors) || (vb2 < 0);
                     n_in = bad ? 0 : ve2 - vb2;
                     src  = p.compressed + (bad ? 0 : vb2);
-#pragma unroll
-                    for (int q = 0; q < CAP; ++q) {
-                        if (q * 32 >= n_in)
-                            break;
-                        if (q * 32 + lane < n_in && !(FLASHLLM_ABLATE & 8))
-                            nxt[q] = ldg_stream16(src + q * 32 + lane);
-                    }
+                    if (!(FLASHLLM_ABLATE & 8))
+                        load_batch<WPT, CAP>(nxt, src + first_vec, n_in, n_in - first_vec);
                     // ... and pull the one after it from DRAM into L2, so that its register loads, issued one tile
                     // from now, only have the L2 latency left to hide
-                    if (lane == 0 && j + kPrefetchAhead * NSW < L) {
-                        const int pb = offs[j + kPrefetchAhead * NSW], pe = offs[j + kPrefetchAhead * NSW + 1];
+                    if (lane == 0 && h == 0 && j + kPrefetchAhead * WARPS < L) {
+                        const int pb = offs[j + kPrefetchAhead * WARPS], pe = offs[j + kPrefetchAhead * WARPS + 1];
                         if (pe > pb)
                             ptx::prefetch_l2_bulk(p.compressed + pb, static_cast<uint32_t>(pe - pb) * 16u);
                     }

@@ -177,6 +177,51 @@ int FlashLLM_SpMM_SplitK_BiasAct(void*       stream,
                                  const void* bias,
                                  int         activation);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * Row-parallel SpMM with the all-reduce fused in (tensor-parallel inference: the attention output projection and
+ * the second feed-forward matmul hold a slice of K on every GPU, so every GPU's product is a partial sum).  The
+ * reference's caller runs the SpMM and then FasterTransformer's NCCL all-reduce (third_party/ft.patch:2822-2846 and
+ * the call sites :1328-1340, :615-633; its custom all-reduce is switched off, :97).  Here the SpMM kernel stores its
+ * fp32 partial sums straight into a receive buffer on every GPU of the group (plain peer stores over NVLink) and
+ * raises a flag per CTA; a second kernel on each GPU waits for all flags (bounded: 200 ms, then status bit 32 and
+ * nothing is stored), adds the partial sums in rank order and rounds once, so every GPU ends with the same bits.
+ * ---------------------------------------------------------------------------------------------------------- */
+
+/* Bytes of one GPU's receive buffer for a group of `world` (1..8) GPUs and outputs of up to `max_elems` = M*N values
+ * (a multiple of 4); 0 for bad arguments. */
+unsigned long long FlashLLM_Comm_BufferBytes(int world, long long max_elems);
+
+/* Allocates (cudaMalloc) and clears this GPU's receive buffer on the current device; with `ipc_handle` != nullptr also
+ * writes the 64-byte inter-process handle (cudaIpcMemHandle_t) other processes open it with. */
+int FlashLLM_Comm_AllocBuffer(int world, long long max_elems, void** buffer, void* ipc_handle);
+/* Maps a peer's buffer (its 64-byte handle) into this process / unmaps it / frees an own buffer. */
+int FlashLLM_Comm_OpenPeerBuffer(const void* ipc_handle, void** buffer);
+int FlashLLM_Comm_ClosePeerBuffer(void* buffer);
+int FlashLLM_Comm_FreeBuffer(void* buffer);
+
+/* A communicator: `buffers[w]` = GPU w's receive buffer as addressable from this process (`buffers[rank]` the own
+ * one).  All GPUs must have allocated (and thereby cleared) their buffers before any of them makes a fused call, and
+ * every GPU must make the same sequence of fused calls on its communicator. */
+int FlashLLM_Comm_Create(void** comm, int rank, int world, long long max_elems, void* const* buffers);
+int FlashLLM_Comm_Destroy(void* comm);
+
+/* C[n][m] = act(sum over the group's GPUs w of sum_k A_w[m][k] * B_w[n][k] + bias[m]) on every GPU.  Arguments as
+ * FlashLLM_SpMM_SplitK_BiasAct without workspace and Split_K (the K cut of one GPU's product stays inside thread-block
+ * clusters).  `phases`: 3 = both kernels (the normal call); 1 = the SpMM and its stores only, 2 = the summing kernel
+ * only -- for a host that drives several GPUs' calls from one thread and wants all sends enqueued before any sum. */
+int FlashLLM_SpMM_SplitK_AllReduce(void*       comm,
+                                   void*       stream,
+                                   const void* Compressed_A,
+                                   const int*  TileOffsets,
+                                   const void* B,
+                                   void*       C,
+                                   int         M,
+                                   int         N,
+                                   int         K,
+                                   const void* bias,
+                                   int         activation,
+                                   int         phases);
+
 /* SpMM for callers that must not allocate device memory.  (No counterpart in the reference, whose callers always
  * bring a Reduction_Workspace of their own.)  Some hosts of this library cannot call cudaMalloc at the point where
  * they need the product: code running while a CUDA graph is being captured, a serving loop whose memory pool was
@@ -227,11 +272,15 @@ void FlashLLM_SetLaunchOverlap(int enable);
  *   4 b_batch         K tiles of B per TMA instruction
  *   5 ring_slots x 6 chunk_vectors (16 bytes each, power of two): the compressed-stream ring (ring form only)
  *   7 scatter_warps   warps that decompress tiles, one whole tile per warp at a time (ring form: 4..12, at most
- *                     a_stages; register-streaming form: 4, two CTAs per SM, or 8, one CTA per SM)
- *   8 producers       warps issuing the bulk copies (ring form only: 1..4; must divide ring_slots)
+ *                     a_stages; register-streaming form: 4, two CTAs per SM, or 8, one CTA per SM; janitor form: 4, 6
+ *                     or 8)
+ *   8 producers       ring form: warps issuing the bulk copies (1..4; must divide ring_slots); register-streaming form
+ *                     with 4 scatter_warps: 2 = two warps share every tile (8 scatter warps on 4 stages)
  *   9 path            1 = ring form: the compressed stream is copied into a shared-memory ring by bulk copies;
  *                     2 = register-streaming form (the default): scatter warps load their tiles' words from global
- *                     memory into registers, tiles alternate between two MMA-issuing threads
+ *                     memory into registers, tiles alternate between two MMA-issuing threads;
+ *                     3 = janitor form: as 2, with stages cleared by a warp of their own and decoupled from the
+ *                     scatter warps (a_stages >= scatter_warps, even)
  * FlashLLM_SetPlan(nullptr, 0) restores automatic choice. */
 void FlashLLM_SetPlan(const int* fields, int count);
 
@@ -240,7 +289,10 @@ void FlashLLM_SetPlan(const int* fields, int count);
 int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count);
 
 /* Reads and clears the device-side status word of the current device (synchronises the device).  0 = no kernel of
- * this library gave up on a bounded wait or met a malformed TileOffsets since the last call. */
+ * this library gave up on a bounded wait or met a malformed TileOffsets since the last call.  Bits: 1 a bounded wait
+ * inside a kernel ran out, 2 malformed TileOffsets (nothing stored for that tile row), 8 device encoder: offsets do not
+ * match the matrix, 16 misaligned shared memory, 32 fused all-reduce: a GPU of the group did not deliver in time.  A
+ * give-up belongs to the launch it happened in: later calls run normally whether or not the word is read. */
 unsigned int FlashLLM_ConsumeStatus(void);
 
 /* Number of kernels this library has launched from this process (all devices). */

@@ -10,9 +10,10 @@ from helpers import DeviceProblem, assert_close, random_problem
 
 pytestmark = pytest.mark.gpu
 
-FORMS = [dict(path=1), dict(path=2, scatter_warps=8), dict(path=2, scatter_warps=4), dict(path=3, scatter_warps=4),
+FORMS = [dict(path=1), dict(path=2, scatter_warps=8), dict(path=2, scatter_warps=4),
+         dict(path=2, scatter_warps=4, producers=2), dict(path=3, scatter_warps=4),
          dict(path=3, scatter_warps=6), dict(path=3, scatter_warps=8), dict(path=3, scatter_warps=4, a_stages=4)]
-FORM_IDS = ["ring", "direct8", "direct4", "janitor4", "janitor6", "janitor8", "janitor4x4"]
+FORM_IDS = ["ring", "direct8", "direct4", "direct4x2", "janitor4", "janitor6", "janitor8", "janitor4x4"]
 
 
 def _check(lib, oracle, A, B, N, split_k, plan, note):
