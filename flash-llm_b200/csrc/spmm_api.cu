@@ -13,7 +13,6 @@
 #include "../../include/SpMM_API.cuh"
 #include "spmm_kernel_direct_sm100.cuh"
 #include "spmm_kernel_sm100.cuh"
-#include "spmm_kernel_janitor_sm100.cuh"
 #include "tiled_csl_host.h"
 #include "tiling.h"
 
@@ -72,19 +71,6 @@ static std::once_flag g_encode_once;
 constexpr int kDirectBlocks = FLASHLLM_DIRECT_BLOCKS;  // CTAs per SM of the 4-stage shapes
 constexpr int kDirectCapWide = 24, kDirectCapNarrow = FLASHLLM_NARROW_CAP, kDirectCapPair = FLASHLLM_PAIR_CAP;
 
-// Rows (32 vectors each) of the continuous-stream kernel's register window, for its three shapes: 4 or 6 scatter
-// warps with two CTAs per SM, 8 scatter warps with one CTA per SM.
-#ifndef FLASHLLM_JANITOR_CAP4
-#define FLASHLLM_JANITOR_CAP4 14
-#endif
-#ifndef FLASHLLM_JANITOR_CAP6
-#define FLASHLLM_JANITOR_CAP6 14
-#endif
-#ifndef FLASHLLM_JANITOR_CAP8
-#define FLASHLLM_JANITOR_CAP8 20
-#endif
-constexpr int kJanitorCap4 = FLASHLLM_JANITOR_CAP4, kJanitorCap6 = FLASHLLM_JANITOR_CAP6, kJanitorCap8 = FLASHLLM_JANITOR_CAP8;
-
 template<typename Kernel>
 static cudaError_t raise_smem_limit_of(Kernel kernel, int optin)
 {
@@ -107,12 +93,6 @@ static cudaError_t raise_smem_limit(int optin)
         e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapNarrow, 4, kDirectBlocks>, optin);
     if (e == cudaSuccess)
         e = raise_smem_limit_of(spmm_tcgen05_direct_kernel<N_TILE, kDirectCapPair, 4, 2, 2>, optin);
-    if (e == cudaSuccess)
-        e = raise_smem_limit_of(spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap4, 4, 2>, optin);
-    if (e == cudaSuccess)
-        e = raise_smem_limit_of(spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap6, 6, 2>, optin);
-    if (e == cudaSuccess)
-        e = raise_smem_limit_of(spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap8, 8, 1>, optin);
     return e;
 }
 
@@ -197,7 +177,7 @@ static int n_tile_for(int N)
 
 static int plan_smem_bytes(const SpmmPlan& pl)
 {
-    const int bars = 8 * (2 * pl.ring_slots + 3 * pl.a_stages + 2 * pl.b_stages + 1) + 16 + 4 * pl.offsets_staged;
+    const int bars = 8 * (2 * pl.ring_slots + 2 * pl.a_stages + 2 * pl.b_stages + 1) + 16 + 4 * pl.offsets_staged;
     return pl.a_stages * kDenseTileBytes + pl.b_stages * pl.b_batch * pl.n_tile * kTileK * 2
            + pl.ring_slots * pl.chunk_vectors * 16 + bars;
 }
@@ -228,8 +208,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // Two pipelines per SM (4 scatter warps, 4 stages each) where they fit; wide-N tiles need the shared memory for
     // their B batches, so they run one deeper pipeline per SM instead.
     pl.path               = ov.v[kPlanPath] ? ov.v[kPlanPath] : kDefaultPath;
-    const bool janitor    = pl.path == kPathJanitor;
-    const bool direct     = pl.path == kPathDirect || janitor;  // both stream the words through registers
+    const bool direct     = pl.path == kPathDirect;
     pl.scatter_warps      = ov.v[kPlanScatterWarps] ? ov.v[kPlanScatterWarps]
                                                     : (direct ? (pl.n_tile <= 64 ? 4 : 8) : (pl.n_tile <= 32 ? 4 : 8));
     const bool two_per_sm = direct ? pl.scatter_warps < 8 : pl.n_tile <= 32;
@@ -247,7 +226,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
             pl.b_batch = (pl.b_batch + kDirectIssuers - 1) / kDirectIssuers * kDirectIssuers;
         pl.a_stages      = pl.scatter_warps;
         // `producers` of the register-streaming form = warps that share one tile (1, or 2 with four stages)
-        pl.producers     = (!janitor && ov.v[kPlanProducers] == 2 && pl.scatter_warps == 4) ? 2 : (janitor ? 0 : 1);
+        pl.producers     = (ov.v[kPlanProducers] == 2 && pl.scatter_warps == 4) ? 2 : 1;
         pl.ring_slots    = 0;
         pl.chunk_vectors = 0;
     }
@@ -261,7 +240,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // distributed shared memory, CTAs co-scheduled) except on small problems, where the second launch costs more
     // than it saves; clusters also take what the workspace cannot.  Replaces the reference's hand-tuned Split_K
     // tables (kernel_benchmark/benchmark.sh:13-15).
-    const int slots     = st->sm_count * (two_per_sm ? ((direct && !janitor && pl.producers == 1) ? kDirectBlocks : 2) : 1);
+    const int slots     = st->sm_count * (two_per_sm ? ((direct && pl.producers == 1) ? kDirectBlocks : 2) : 1);
     const int max_extra = ((static_cast<long long>(M) * N) % 4 != 0) ? 1 : (Split_K / 2 > 1 ? Split_K / 2 : 1);
     // (with launch overlap on, the second kernel hides behind its neighbours and workspace parts win at every size)
     const bool small    = static_cast<long long>(tile_rows) * k_tiles <= 4096
@@ -302,26 +281,6 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     // room for this CTA's slice of TileOffsets (K tiles of the longest part, plus one), up to 8 KB
     const int longest = (k_tiles + pl.cluster_k * pl.workspace_k - 1) / (pl.cluster_k * pl.workspace_k) + 1;
     pl.offsets_staged = longest + 1 <= 2048 ? ((longest + 1 + 3) / 4) * 4 : 0;
-    if (janitor) {
-        // Stages beyond one per scatter warp let a warp go on with its next tile while the one it published is still
-        // being multiplied and cleared: half as many again where the shared memory of the SM (shared by two CTAs, or
-        // one) has room, an even number so that a stage is always served by the same MMA issuer.
-        pl.a_stages = pl.scatter_warps;
-        if (ov.v[kPlanAStages])
-            pl.a_stages = ov.v[kPlanAStages];
-        else {
-            const int per_cta = two_per_sm ? (st->smem_optin + 1024) / 2 - 1024 : st->smem_optin;
-            const int want    = (pl.scatter_warps + pl.scatter_warps / 2) / kDirectIssuers * kDirectIssuers;
-            for (int a = want; a > pl.scatter_warps; a -= kDirectIssuers) {
-                SpmmPlan trial = pl;
-                trial.a_stages = a;
-                if (a <= kMaxAStages && plan_smem_bytes(trial) <= per_cta) {
-                    pl.a_stages = a;
-                    break;
-                }
-            }
-        }
-    }
     pl.smem_bytes     = plan_smem_bytes(pl);
 
     const bool ring_ok = pl.scatter_warps >= 4 && pl.scatter_warps <= kMaxScatterWarps
@@ -334,13 +293,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
                          && pl.ring_slots * pl.chunk_vectors >= kMaxTileVectors + pl.chunk_vectors;
     const bool direct_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 8)
                            && pl.a_stages == pl.scatter_warps && pl.b_batch % kDirectIssuers == 0;
-    // a stage's successive tiles go to the same MMA issuer, and a warp never waits for a stage two uses ahead: both keep
-    // every mbarrier parity wait within one phase
-    const bool janitor_ok = (pl.scatter_warps == 4 || pl.scatter_warps == 6 || pl.scatter_warps == 8)
-                           && pl.a_stages >= pl.scatter_warps && pl.a_stages % kDirectIssuers == 0
-                           && pl.b_batch % kDirectIssuers == 0;
-    const bool ok = (pl.path == kPathRing || pl.path == kPathDirect || janitor)
-                    && (janitor ? janitor_ok : (direct ? direct_ok : ring_ok))
+    const bool ok = (pl.path == kPathRing || pl.path == kPathDirect) && (direct ? direct_ok : ring_ok)
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
                     && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
@@ -360,9 +313,8 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
     cudaLaunchConfig_t  cfg{};
     cudaLaunchAttribute attr[2];
     cfg.gridDim          = dim3(pl.cluster_k, tile_rows, n_tiles * pl.workspace_k);
-    cfg.blockDim         = dim3((pl.path == kPathJanitor   ? 2 + kDirectIssuers + pl.scatter_warps
-                                 : pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps * pl.producers
-                                                          : pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
+    cfg.blockDim         = dim3((pl.path == kPathDirect ? 1 + kDirectIssuers + pl.scatter_warps * pl.producers
+                                                        : pl.producers + 2 + pl.scatter_warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = pl.smem_bytes;
     cfg.stream           = stream;
     attr[0].id               = cudaLaunchAttributeClusterDimension;
@@ -377,13 +329,6 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
         cfg.numAttrs                                       = 2;
     }
     count_launch();
-    if (pl.path == kPathJanitor) {
-        if (pl.scatter_warps == 8)
-            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap8, 8, 1>, tmap, params);
-        if (pl.scatter_warps == 6)
-            return cudaLaunchKernelEx(&cfg, spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap6, 6, 2>, tmap, params);
-        return cudaLaunchKernelEx(&cfg, spmm_tcgen05_janitor_kernel<N_TILE, kJanitorCap4, 4, 2>, tmap, params);
-    }
     if (pl.path == kPathDirect) {
         if (pl.scatter_warps == 8)
             return cudaLaunchKernelEx(&cfg, spmm_tcgen05_direct_kernel<N_TILE, kDirectCapWide, 8, 1>, tmap, params);

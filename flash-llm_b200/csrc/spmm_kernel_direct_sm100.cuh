@@ -50,6 +50,21 @@ __device__ __forceinline__ void scatter_row_if(uint32_t stage, const uint4& w, i
 {
     const uint32_t a0 = stage + ((w.x >> 15) & 0x3FFEu), a1 = stage + ((w.y >> 15) & 0x3FFEu);
     const uint32_t a2 = stage + ((w.z >> 15) & 0x3FFEu), a3 = stage + ((w.w >> 15) & 0x3FFEu);
+#if (FLASHLLM_ABLATE & 32)  // timing only: whole-word stores in place of the 16-bit ones (neighbours get clobbered)
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.gt.s32 p, %8, %9;\n"
+        "@p st.shared.u32 [%0], %4;\n"
+        "@p st.shared.u32 [%1], %5;\n"
+        "@p st.shared.u32 [%2], %6;\n"
+        "@p st.shared.u32 [%3], %7;\n"
+        "}\n" ::"r"(a0 & ~3u),
+        "r"(a1 & ~3u), "r"(a2 & ~3u), "r"(a3 & ~3u), "r"(w.x << 16), "r"(w.y << 16), "r"(w.z << 16), "r"(w.w << 16), "r"(rem),
+        "n"(VEC_OFFSET)
+        : "memory");
+    return;
+#endif
     asm volatile(
         "{\n"
         ".reg .pred p;\n"

@@ -39,17 +39,15 @@ enum PlanField {
     kPlanChunkVectors,    // ... of this many 16-byte vectors (power of two)
     kPlanScatterWarps,    // warps that decompress tiles, one whole tile per warp at a time (4..12, <= a_stages)
     kPlanProducers,       // warps issuing the bulk copies
-    kPlanPath,            // how compressed words reach the scatter warps: kPathRing, kPathDirect or kPathJanitor
+    kPlanPath,            // how compressed words reach the scatter warps: kPathRing or kPathDirect
     kPlanFieldCount
 };
 
 constexpr int kPathRing   = 1;  // bulk copies into a shared-memory ring (spmm_tcgen05_kernel)
 constexpr int kPathDirect = 2;  // global loads into the scatter warps' registers (spmm_tcgen05_direct_kernel)
-constexpr int kPathJanitor = 3;  // a rolling register window over each scatter warp's tiles, stages cleared by a
-                                // janitor warp (spmm_tcgen05_janitor_kernel)
 
 struct SpmmPlan {
-    int path;    // kPathRing, kPathDirect or kPathJanitor
+    int path;    // kPathRing or kPathDirect
     int n_tile;  // MMA N: 16, 32, 64 or 128
     int cluster_k;
     int workspace_k;

@@ -272,15 +272,12 @@ void FlashLLM_SetLaunchOverlap(int enable);
  *   4 b_batch         K tiles of B per TMA instruction
  *   5 ring_slots x 6 chunk_vectors (16 bytes each, power of two): the compressed-stream ring (ring form only)
  *   7 scatter_warps   warps that decompress tiles, one whole tile per warp at a time (ring form: 4..12, at most
- *                     a_stages; register-streaming form: 4, two CTAs per SM, or 8, one CTA per SM; janitor form: 4, 6
- *                     or 8)
+ *                     a_stages; register-streaming form: 4, two CTAs per SM, or 8, one CTA per SM)
  *   8 producers       ring form: warps issuing the bulk copies (1..4; must divide ring_slots); register-streaming form
  *                     with 4 scatter_warps: 2 = two warps share every tile (8 scatter warps on 4 stages)
  *   9 path            1 = ring form: the compressed stream is copied into a shared-memory ring by bulk copies;
  *                     2 = register-streaming form (the default): scatter warps load their tiles' words from global
- *                     memory into registers, tiles alternate between two MMA-issuing threads;
- *                     3 = janitor form: as 2, with stages cleared by a warp of their own and decoupled from the
- *                     scatter warps (a_stages >= scatter_warps, even)
+ *                     memory into registers, tiles alternate between two MMA-issuing threads
  * FlashLLM_SetPlan(nullptr, 0) restores automatic choice. */
 void FlashLLM_SetPlan(const int* fields, int count);
 
