@@ -646,6 +646,7 @@ def run_tp_chain(args) -> None:
     del full
 
     def parity_of(run_step) -> list:
+        ranks.barrier()  # the fused call waits for its partners for a bounded time only: start the ranks together
         out = run_step().clone()
         torch.cuda.synchronize(dev)
         status = fl.consume_status()

@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     comm_destroy,
     comm_free_buffer,
     comm_open_peer_buffer,
+    comm_set_wait_limit,
     consume_status,
     encode_on_device,
     gen_sparse_matrix_bin_file_device,

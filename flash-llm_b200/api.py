@@ -84,6 +84,8 @@ def library() -> C.CDLL:
         f = getattr(L, name)
         f.restype = C.c_int
         f.argtypes = [C.c_void_p]
+    L.FlashLLM_Comm_SetWaitLimit.restype = C.c_int
+    L.FlashLLM_Comm_SetWaitLimit.argtypes = [C.c_void_p, C.c_int]
     L.FlashLLM_Comm_Create.restype = C.c_int
     L.FlashLLM_Comm_Create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_longlong, C.POINTER(C.c_void_p)]
     L.FlashLLM_SpMM_SplitK_AllReduce.restype = C.c_int
@@ -287,6 +289,11 @@ def comm_create(rank: int, world: int, max_elems: int, buffers: list[int]):
     arr = (C.c_void_p * world)(*buffers)
     _check(library().FlashLLM_Comm_Create(C.byref(comm), rank, world, max_elems, arr), "Comm_Create")
     return comm
+
+
+def comm_set_wait_limit(comm, milliseconds: int) -> None:
+    """How long the summing kernel waits for the slowest rank before giving up with status bit 32 (default 2000 ms)."""
+    _check(library().FlashLLM_Comm_SetWaitLimit(comm, milliseconds), "Comm_SetWaitLimit")
 
 
 def comm_destroy(comm) -> None:

@@ -393,6 +393,10 @@ struct FlashLLMComm {
     long long      max_elems = 0;
     unsigned char* buffer[kMaxPushWorld] = {nullptr};  // buffer[w]: GPU w's receive buffer as mapped in this process
     unsigned int   epoch = 0;                          // calls made so far; every GPU of the group makes the same calls
+    // How long the summing kernel waits for the slowest GPU of the group before it gives up (status bit 32).  The
+    // GPUs of a group enter a layer at slightly different times; the limit only has to end a wait for a partner that
+    // never comes.
+    unsigned long long wait_limit_ns = 2000ull * 1000ull * 1000ull;
 };
 
 static size_t comm_slot_bytes(int world, long long max_elems)
@@ -531,7 +535,8 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
         count_launch();
         return cudaLaunchKernelEx(&cfg, allreduce_sum_kernel, C, reinterpret_cast<const float*>(mine + set_slots),
                                   comm->max_elems, reinterpret_cast<const unsigned int*>(mine + set_flags), kCommFlagsPerRank,
-                                  comm->epoch, comm->world, grid_ctas, count, bias, M_Global, activation, st->status);
+                                  comm->epoch, comm->world, grid_ctas, count, bias, M_Global, activation, st->status,
+                                  comm->wait_limit_ns);
     }
     if (pl.workspace_k > 1)
         return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k,
@@ -696,6 +701,14 @@ int FlashLLM_Comm_Create(void** comm, int rank, int world, long long max_elems, 
     return 0;
 }
 
+int FlashLLM_Comm_SetWaitLimit(void* comm, int milliseconds)
+{
+    if (comm == nullptr || milliseconds < 1 || milliseconds > 60000)
+        return static_cast<int>(cudaErrorInvalidValue);
+    static_cast<FlashLLMComm*>(comm)->wait_limit_ns = static_cast<unsigned long long>(milliseconds) * 1000000ull;
+    return 0;
+}
+
 int FlashLLM_Comm_Destroy(void* comm)
 {
     delete static_cast<FlashLLMComm*>(comm);
@@ -779,6 +792,15 @@ unsigned int FlashLLM_ConsumeStatus(void)
         cudaMemset(st->status, 0, sizeof(value));
     return value;
 }
+
+#ifdef FLASHLLM_CTA_TIMES
+// Launch-shape builds only: copies the per-CTA stamps (4 per CTA, up to 4096 CTAs) to the host.
+int FlashLLM_DebugCtaTimes(unsigned long long* out, int count)
+{
+    cudaDeviceSynchronize();
+    return static_cast<int>(cudaMemcpyFromSymbol(out, flashllm::g_cta_times, sizeof(unsigned long long) * count));
+}
+#endif
 
 #ifdef FLASHLLM_TRACE
 // Timeline builds only: copies the recorded timestamps (kinds x depth) to the host.

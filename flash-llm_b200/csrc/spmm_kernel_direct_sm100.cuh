@@ -163,6 +163,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0)
+        FL_CTA_TIME(0);
 
     const SpmmPlan& plan     = p.plan;
     const int       b_stages = plan.b_stages;
@@ -249,6 +251,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
     // (in its B loader) before it touches anything this grid or its predecessors produce.
     if (threadIdx.x == 0)
         ptx::grid_launch_dependents();
+    if (threadIdx.x == 0)
+        FL_CTA_TIME(1);
 
     if (warp == b_warp) {
         // ================================================================ B loader: KB K tiles per TMA instruction
@@ -358,15 +362,6 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
             }
             uint32_t use = 0;
             for (int j = st; j < L; j += WARPS, ++use) {
-                // Offsets of this warp's following tile, fetched a whole tile ahead of their use: read after the proxy
-                // fence below, they would wait for it, and the loads that need them would wait for them (measured: the
-                // refill then takes ~7000 cycles instead of ~650).
-                const bool has_next = j + WARPS < L;
-                int        vb2 = 0, ve2 = 0;
-                if (has_next) {
-                    vb2 = offs[j + WARPS];
-                    ve2 = offs[j + WARPS + 1];
-                }
                 if (bad)
                     atomicOr(p.status, kStatusBadTileOffsets);
                 if (lane == 0)
@@ -381,6 +376,16 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                 }
                 if (lane == 0)
                     FL_TRACE(3, j);
+                // Offsets of this warp's following tile.  Two places are wrong for these two shared-memory loads: right
+                // behind the previous tile's global loads (they queue behind them in the load/store unit: ~700 cycles at
+                // the loop's top) and behind the proxy fence below (they wait for it, and the loads that need them wait
+                // for them: the refill then takes ~7000 cycles instead of ~650).  Here the unit is idle.
+                const bool has_next = j + WARPS < L;
+                int        vb2 = 0, ve2 = 0;
+                if (has_next) {
+                    vb2 = offs[j + WARPS];
+                    ve2 = offs[j + WARPS + 1];
+                }
                 // ---- clear the stage (each sharing warp its part), then scatter the new tile
                 if (!(FLASHLLM_ABLATE & 1)) {
 #pragma unroll
@@ -412,6 +417,7 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                 }
                 if (lane == 0)
                     FL_TRACE(5, j);
+#ifndef FLASHLLM_FETCH_FIRST
 #if !(FLASHLLM_ABLATE & 16)  // timing only: without the proxy fence the tensor core may read stale words
                 ptx::fence_proxy_async_smem();
 #endif
@@ -420,6 +426,7 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                     ptx::mbar_arrive(full_bar);
                 if (lane == 0)
                     FL_TRACE(6, j);
+#endif
                 // ---- start fetching the following tile
                 if (has_next) {
                     bad  = (ve2 < vb2) || (ve2 - vb2 > kMaxTileVectors) || (vb2 < 0);
@@ -435,6 +442,14 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                             ptx::prefetch_l2_bulk(p.compressed + pb, static_cast<uint32_t>(pe - pb) * 16u);
                     }
                 }
+#ifdef FLASHLLM_FETCH_FIRST
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(full_bar);
+                if (lane == 0)
+                    FL_TRACE(6, j);
+#endif
                 if (lane == 0)
                     FL_TRACE(13, j);
             }
@@ -446,6 +461,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
             acc_ok = wait_bounded_warp(acc_full, 0u, abort_flag, p.status);
         acc_ok = __all_sync(0xFFFFFFFFu, acc_ok && (*abort_flag == 0u));
         ptx::tc_fence_after_sync();
+        if (sw == 0 && lane == 0)
+            FL_CTA_TIME(2);
 
         accumulators_to_output<N_TILE>(p, tmem_acc, L < MI ? L : MI, N_TILE, warp & 3, lane, sw, NSW >= 8 ? 2 : 1, S, G, g,
                                        n_idx, tile_row, acc_ok, reinterpret_cast<float*>(smem));
@@ -464,6 +481,8 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
         ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     }
     push_raise_flags(p, *abort_flag == 0u);
+    if (threadIdx.x == 0)
+        FL_CTA_TIME(3);
     if (warp == mma_warp) {
         __syncwarp();
         ptx::tmem_dealloc(tmem_acc, kTmemCols);

@@ -102,6 +102,22 @@ __device__ long long g_trace_origin;
     } while (0)
 #endif
 
+// Launch-shape builds (never the shipped one) record four wall-clock stamps per CTA: entry, set-up done, accumulators
+// complete, exit.
+#ifdef FLASHLLM_CTA_TIMES
+__device__ unsigned long long g_cta_times[4 * 4096];
+#define FL_CTA_TIME(slot)                                                                                               \
+    do {                                                                                                               \
+        const unsigned int cta_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;                      \
+        if (cta_ < 4096u)                                                                                              \
+            g_cta_times[4u * cta_ + (slot)] = ptx::globaltimer_ns();                                                   \
+    } while (0)
+#else
+#define FL_CTA_TIME(slot)                                                                                               \
+    do {                                                                                                               \
+    } while (0)
+#endif
+
 // Spins on one mbarrier phase.  Returns false when the CTA has been told to give up, or after kWaitLimitNs,
 // in which case it raises the abort flag and the status bit itself.
 __device__ __forceinline__ bool
@@ -912,13 +928,13 @@ constexpr unsigned kStatusPeerWaitExpired = 32u;  // a GPU of the group did not 
 // Fused all-reduce, receiving side: C = fp16(act(sum over the group's GPUs of their fp32 partial products + bias)).
 // `slots` holds `world` matrices [N][M] fp32, `slot_stride` floats apart (slot w written by GPU w); `flags` holds, for
 // each sender, `flag_stride` words of which the first `flags_per_rank` are in use (one per CTA of the sending grid).
-// Before a CTA reads anything it waits, bounded, until every flag of every sender has reached `epoch` (a sender raises
+// Before a CTA reads anything it waits, for at most `wait_limit_ns`, until every flag of every sender has reached `epoch` (a sender raises
 // a flag after the stores of one CTA, so all of them together cover the whole matrix).  Slots are added in rank order
 // on every GPU, so all GPUs get the same bits.
 __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, long long slot_stride,
                                      const unsigned int* flags, int flag_stride, unsigned int epoch, int world,
                                      int flags_per_rank, long long count, const half* __restrict__ bias, int M,
-                                     int activation, unsigned int* status)
+                                     int activation, unsigned int* status, unsigned long long wait_limit_ns)
 {
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
@@ -940,7 +956,7 @@ __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, l
                 const uint64_t now = ptx::globaltimer_ns();
                 if (t0 == 0)
                     t0 = now;
-                else if (now - t0 > kWaitLimitNs) {
+                else if (now - t0 > wait_limit_ns) {
                     mine_ok = false;
                     break;
                 }

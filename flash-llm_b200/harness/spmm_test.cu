@@ -18,6 +18,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <thread>
+#include <string>
 #include <vector>
 
 #include "../../include/SpMM_API.cuh"
@@ -85,11 +86,46 @@ static float time_spmm(SpmmFn fn, const uint4* nz, const int* offs, const half* 
 int main(int argc, char** argv)
 {
     if (argc < 6) {
-        printf("Wrong Inputs! Correct input format: ./spmm_test M K N Sparsity SplitK [--ref path/to/reference.so]\n");
+        printf("Wrong Inputs! Correct input format: ./spmm_test M K N Sparsity SplitK [--ref path/to/reference.so] [--plan name=value,...]\n");
         return 1;
     }
     const int   M = atoi(argv[1]), K = atoi(argv[2]), N = atoi(argv[3]), sparsity_pct = atoi(argv[4]), split_k = atoi(argv[5]);
-    const char* ref_path = (argc >= 8 && strcmp(argv[6], "--ref") == 0) ? argv[7] : nullptr;
+    // optional, in any order after the five numbers: --ref <reference .so>, --plan name=value[,name=value...]
+    // (the fields of FlashLLM_SetPlan: cluster_k, workspace_k, a_stages, b_stages, b_batch, ring_slots, chunk_vectors,
+    // scatter_warps, producers, path)
+    const char* ref_path = nullptr;
+    for (int a = 6; a + 1 < argc; a += 2) {
+        if (strcmp(argv[a], "--ref") == 0)
+            ref_path = argv[a + 1];
+        else if (strcmp(argv[a], "--plan") == 0) {
+            static const char* names[10] = {"cluster_k",  "workspace_k",   "a_stages",      "b_stages",  "b_batch",
+                                            "ring_slots", "chunk_vectors", "scatter_warps", "producers", "path"};
+            int                fields[10] = {0};
+            std::string        spec(argv[a + 1]);
+            size_t             pos = 0;
+            while (pos < spec.size()) {
+                const size_t end = spec.find(',', pos);
+                const std::string item = spec.substr(pos, end == std::string::npos ? std::string::npos : end - pos);
+                const size_t eq = item.find('=');
+                bool known = false;
+                for (int f = 0; f < 10 && eq != std::string::npos; ++f)
+                    if (item.compare(0, eq, names[f]) == 0) {
+                        fields[f] = atoi(item.c_str() + eq + 1);
+                        known     = true;
+                    }
+                if (!known) {
+                    printf("unknown plan field in '%s'\n", item.c_str());
+                    return 1;
+                }
+                pos = end == std::string::npos ? spec.size() : end + 1;
+            }
+            FlashLLM_SetPlan(fields, 10);
+        }
+        else {
+            printf("unknown option %s\n", argv[a]);
+            return 1;
+        }
+    }
     const float sparsity = sparsity_pct / 100.0f;
     const uint64_t seed_a = 0xF1A50000ull + static_cast<uint64_t>(sparsity_pct), seed_b = seed_a ^ 0xB;
 

@@ -183,8 +183,8 @@ int FlashLLM_SpMM_SplitK_BiasAct(void*       stream,
  * reference's caller runs the SpMM and then FasterTransformer's NCCL all-reduce (third_party/ft.patch:2822-2846 and
  * the call sites :1328-1340, :615-633; its custom all-reduce is switched off, :97).  Here the SpMM kernel stores its
  * fp32 partial sums straight into a receive buffer on every GPU of the group (plain peer stores over NVLink) and
- * raises a flag per CTA; a second kernel on each GPU waits for all flags (bounded: 200 ms, then status bit 32 and
- * nothing is stored), adds the partial sums in rank order and rounds once, so every GPU ends with the same bits.
+ * raises a flag per CTA; a second kernel on each GPU waits for all flags (bounded: 2 s unless set otherwise, then status
+ * bit 32 and nothing is stored), adds the partial sums in rank order and rounds once, so every GPU ends with the same bits.
  * ---------------------------------------------------------------------------------------------------------- */
 
 /* Bytes of one GPU's receive buffer for a group of `world` (1..8) GPUs and outputs of up to `max_elems` = M*N values
@@ -204,6 +204,10 @@ int FlashLLM_Comm_FreeBuffer(void* buffer);
  * every GPU must make the same sequence of fused calls on its communicator. */
 int FlashLLM_Comm_Create(void** comm, int rank, int world, long long max_elems, void* const* buffers);
 int FlashLLM_Comm_Destroy(void* comm);
+/* How long the summing kernel waits for the slowest GPU of the group before it gives up with status bit 32:
+ * 1..60000 ms, 2000 ms unless set.  GPUs enter a layer at slightly different times; the limit only has to end the
+ * wait for a partner that never comes. */
+int FlashLLM_Comm_SetWaitLimit(void* comm, int milliseconds);
 
 /* C[n][m] = act(sum over the group's GPUs w of sum_k A_w[m][k] * B_w[n][k] + bias[m]) on every GPU.  Arguments as
  * FlashLLM_SpMM_SplitK_BiasAct without workspace and Split_K (the K cut of one GPU's product stays inside thread-block

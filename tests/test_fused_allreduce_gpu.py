@@ -77,7 +77,7 @@ def test_fused_allreduce_applies_bias_and_relu_after_the_sum(lib, oracle):
 
 
 def test_missing_peer_is_reported_not_waited_for(lib):
-    """A rank whose partner never delivers: the summing kernel's wait is bounded (200 ms), it then sets status bit 32,
+    """A rank whose partner never delivers: the summing kernel's wait is bounded (set to 200 ms here), it then sets status bit 32,
     stores nothing and returns; the context stays usable.  The missing delivery is made on the host (the partner's call
     is simply not issued); nothing on the device faults or spins without a limit."""
     from flash_llm_b200 import tp_chain
@@ -85,6 +85,7 @@ def test_missing_peer_is_reported_not_waited_for(lib):
     _, _, parts, k = _shards(lib, M, K_full, N, world, seed=5)
     stream = torch.cuda.current_stream().cuda_stream
     group = tp_chain.LocalGroup(lib, world, M * N)
+    lib.comm_set_wait_limit(group.comms[0], 200)
     try:
         out = torch.full((N, M), 7.0, dtype=torch.float16, device="cuda")
         comp, offs, B_r = parts[0]
