@@ -210,6 +210,30 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
         return;
     }
 
+    // ---- scatter warps: the first tile's words are requested before anything else, so that the set-up below
+    // (barrier initialisation, tensor-memory allocation, offset staging and checking: ~1.5 us) hides behind their
+    // latency instead of preceding it.  The two offsets are read straight from global memory and checked on the spot.
+    const int sw        = warp - first_sw;
+    const int st        = sw % WARPS;       // the stage, and the tile stream st, st + WARPS, ... this warp works on
+    const int h         = sw / WARPS;       // its index among the WPT warps that share those tiles
+    const int first_vec = h * 32 + lane;    // this lane's vector in row 0 of the warp's share
+    uint4     nxt[CAP];                     // words of the tile about to be scattered (loads in flight)
+    int          n_in = 0;                  // vectors of the whole tile whose share is in nxt
+    const uint4* src  = p.compressed;
+    bool         bad  = false;
+    if (warp >= first_sw) {
+#pragma unroll
+        for (int q = 0; q < CAP; ++q)
+            nxt[q] = make_uint4(0u, 0u, 0u, 0u);
+        if (st < L) {
+            const int vb = offs_global[st], ve = offs_global[st + 1];
+            bad          = (ve < vb) || (ve - vb > kMaxTileVectors) || (vb < 0);
+            n_in         = bad ? 0 : ve - vb;
+            src          = p.compressed + (bad ? 0 : vb);
+            load_batch<WPT, CAP>(nxt, src + first_vec, n_in, n_in - first_vec);
+        }
+    }
+
     // ---- set-up
     if (threadIdx.x == 0) {
         for (int i = 0; i < a_stages; ++i) {
@@ -329,35 +353,16 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
     }
     else {
         // ================================================================ scatter warps: WPT warps per stage
-        const int sw = warp - first_sw;
-        const int st = sw % WARPS;  // the stage, and the tile stream st, st + WARPS, ... this warp works on
-        const int h  = sw / WARPS;  // its index among the WPT warps that share those tiles
         if (L > 0 && go) {
             const uint32_t stage     = a_base + st * kDenseTileBytes;
             const uint32_t full_bar  = a_full + 8u * st;
             const uint32_t empty_bar = a_empty + 8u * st;
-            const int      first_vec = h * 32 + lane;  // this lane's vector in row 0 of the warp's share
-            uint4          nxt[CAP];                   // words of the tile about to be scattered (loads in flight)
-#pragma unroll
-            for (int q = 0; q < CAP; ++q)
-                nxt[q] = make_uint4(0u, 0u, 0u, 0u);
-
-            int          n_in = 0;  // vectors of the whole tile whose share is in nxt
-            const uint4* src  = p.compressed;
-            bool         bad  = false;
-            // ---- first tile of this warp
-            if (st < L) {
-                const int vb = offs[st], ve = offs[st + 1];
-                bad          = (ve < vb) || (ve - vb > kMaxTileVectors) || (vb < 0);
-                n_in         = bad ? 0 : ve - vb;
-                src          = p.compressed + (bad ? 0 : vb);
-                load_batch<WPT, CAP>(nxt, src + first_vec, n_in, n_in - first_vec);
-                if (lane == 0 && h == 0) {
-                    for (int a = 1; a < kPrefetchAhead; ++a) {
-                        const int t = st + a * WARPS;
-                        if (t < L && offs[t + 1] > offs[t])
-                            ptx::prefetch_l2_bulk(p.compressed + offs[t], static_cast<uint32_t>(offs[t + 1] - offs[t]) * 16u);
-                    }
+            // the tile after the first one is pulled from DRAM into L2 (its register loads come one tile from now)
+            if (st < L && lane == 0 && h == 0) {
+                for (int a = 1; a < kPrefetchAhead; ++a) {
+                    const int t = st + a * WARPS;
+                    if (t < L && offs[t + 1] > offs[t])
+                        ptx::prefetch_l2_bulk(p.compressed + offs[t], static_cast<uint32_t>(offs[t + 1] - offs[t]) * 16u);
                 }
             }
             uint32_t use = 0;
@@ -387,11 +392,20 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                     ve2 = offs[j + WARPS + 1];
                 }
                 // ---- clear the stage (each sharing warp its part), then scatter the new tile
+#ifdef FLASHLLM_ZERO_BULK
+                // experiment: one bulk zero-initialising store per participating lane instead of 32 vector stores
+                if (lane < FLASHLLM_ZERO_BULK)
+                    asm volatile("st.bulk.weak.shared::cta [%0], %1, 0;" ::"r"(
+                                     stage + static_cast<uint32_t>(h * FLASHLLM_ZERO_BULK + lane) * (kDenseTileBytes / (FLASHLLM_ZERO_BULK * WPT))),
+                                 "l"(static_cast<unsigned long long>(kDenseTileBytes / (FLASHLLM_ZERO_BULK * WPT)))
+                                 : "memory");
+#else
                 if (!(FLASHLLM_ABLATE & 1)) {
 #pragma unroll
                     for (int q = 0; q < 32 / WPT; ++q)
                         sts_zero16(stage + static_cast<uint32_t>((q * WPT + h) * 32 + lane) * 16u);
                 }
+#endif
                 // another lane's (or the partner warp's) zero must not land on top of a new value
                 if (WPT == 1)
                     __syncwarp();

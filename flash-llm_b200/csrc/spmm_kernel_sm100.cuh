@@ -307,13 +307,24 @@ __device__ __forceinline__ void accumulators_to_output(const SpmmParams& p, uint
 #pragma unroll
         for (int i = 0; i < 8; ++i)
             r[i] = 0.0f;
-        for (int a = 0; a < accumulators; ++a) {
-            uint32_t t[8];
-            ptx::tmem_ld_x8(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + a * acc_stride + c0, t);
+        if (accumulators == 2) {  // the two loads go out together and are waited for once
+            uint32_t t0[8], t1[8];
+            ptx::tmem_ld_x8(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, t0);
+            ptx::tmem_ld_x8(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + acc_stride + c0, t1);
             ptx::tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                r[i] += __uint_as_float(t[i]);
+                r[i] = __uint_as_float(t0[i]) + __uint_as_float(t1[i]);
+        }
+        else {
+            for (int a = 0; a < accumulators; ++a) {
+                uint32_t t[8];
+                ptx::tmem_ld_x8(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + a * acc_stride + c0, t);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    r[i] += __uint_as_float(t[i]);
+            }
         }
         if (S == 1) {
             if (acc_ok) {
