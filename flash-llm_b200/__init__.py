@@ -35,6 +35,7 @@ from .api import (  # noqa: F401
     set_plan,
     splitk_reduction,
     spmm_splitk_bias_act,
+    spmm_splitk_epilogue,
     spmm_splitk_allreduce,
     spmm_splitk_no_alloc,
     write_rank_lists,

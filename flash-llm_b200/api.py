@@ -49,6 +49,9 @@ def library() -> C.CDLL:
     L.FlashLLM_SpMM_SplitK.argtypes = [C.c_void_p] * 3 + [C.c_void_p] * 3 + [C.c_int] * 3 + [C.c_void_p, C.c_int]
     L.FlashLLM_SpMM_SplitK_BiasAct.restype = C.c_int
     L.FlashLLM_SpMM_SplitK_BiasAct.argtypes = ([C.c_void_p] * 5 + [C.c_int] * 3 + [C.c_void_p, C.c_int, C.c_void_p, C.c_int])
+    L.FlashLLM_SpMM_SplitK_Epilogue.restype = C.c_int
+    L.FlashLLM_SpMM_SplitK_Epilogue.argtypes = ([C.c_void_p] * 5 + [C.c_int] * 3
+                                                + [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p])
     for name in ("FlashLLM_InitSparseMatrixA", "FlashLLM_InitSparseMatrixA_NoReorder"):
         f = getattr(L, name)
         f.restype = C.c_int
@@ -89,7 +92,7 @@ def library() -> C.CDLL:
     L.FlashLLM_Comm_Create.restype = C.c_int
     L.FlashLLM_Comm_Create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_longlong, C.POINTER(C.c_void_p)]
     L.FlashLLM_SpMM_SplitK_AllReduce.restype = C.c_int
-    L.FlashLLM_SpMM_SplitK_AllReduce.argtypes = [C.c_void_p] * 6 + [C.c_int] * 3 + [C.c_void_p, C.c_int, C.c_int]
+    L.FlashLLM_SpMM_SplitK_AllReduce.argtypes = [C.c_void_p] * 6 + [C.c_int] * 3 + [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
     L.FlashLLM_SplitK_Reduction.restype = C.c_int
     L.FlashLLM_SplitK_Reduction.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
     L.FlashLLM_SetLaunchOverlap.argtypes = [C.c_int]
@@ -241,6 +244,17 @@ def spmm_splitk_bias_act(stream: int, Compressed_A: int, TileOffsets: int, B: in
     _check(code, f"SpMM_SplitK_BiasAct(M={M}, N={N}, K={K}, Split_K={Split_K})")
 
 
+def spmm_splitk_epilogue(stream: int, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int, N: int, K: int,
+                         Reduction_Workspace: int | None, Split_K: int, bias: int | None = None,
+                         activation: int = ACT_NONE, residual: int | None = None) -> None:
+    """``C[N][M] = act(B @ A^T + bias[M]) + residual[N][M]``, all on the fp32 sums before the one fp16 rounding (the
+    add-bias-residual step a decoder layer runs after its attention output projection and its second feed-forward
+    matmul).  ``residual`` is a device matrix laid out like C that does not overlap it, or ``None``."""
+    code = library().FlashLLM_SpMM_SplitK_Epilogue(stream, Compressed_A, TileOffsets, B, C_out, M, N, K,
+                                                   Reduction_Workspace, Split_K, bias, activation, residual)
+    _check(code, f"SpMM_SplitK_Epilogue(M={M}, N={N}, K={K}, Split_K={Split_K})")
+
+
 def spmm_splitk_no_alloc(stream: int, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int, N: int, K: int,
                          Split_K: int) -> None:
     """SpMM for callers that may not allocate device memory (graph capture in progress, a fully pre-assigned
@@ -301,14 +315,16 @@ def comm_destroy(comm) -> None:
 
 
 def spmm_splitk_allreduce(comm, stream: int, Compressed_A: int, TileOffsets: int, B: int, C_out: int, M: int, N: int,
-                          K: int, bias: int | None = None, activation: int = ACT_NONE, phases: int = 3) -> None:
-    """Row-parallel SpMM with the all-reduce fused in: ``C[N][M] = act(sum over the group of (B_w @ A_w^T) + bias)``,
+                          K: int, bias: int | None = None, activation: int = ACT_NONE, phases: int = 3,
+                          residual: int | None = None) -> None:
+    """Row-parallel SpMM with the all-reduce fused in: ``C[N][M] = act(sum over the group of (B_w @ A_w^T) + bias)
+    + residual``,
     where this rank holds the K slice ``A_w[M][K]``, ``B_w[N][K]``.  Every rank's kernel stores its fp32 partial sums
     straight into all ranks' receive buffers; a second kernel adds them in rank order and rounds once, so every rank
     ends with the same bits.  ``phases``: 3 = both kernels (the normal call), 1 = the SpMM and its stores only,
     2 = the summing kernel only (for driving several ranks from one stream: all ranks' phase 1, then their phase 2)."""
     code = library().FlashLLM_SpMM_SplitK_AllReduce(comm, stream, Compressed_A, TileOffsets, B, C_out, M, N, K, bias,
-                                                    activation, phases)
+                                                    activation, residual, phases)
     _check(code, f"SpMM_SplitK_AllReduce(M={M}, N={N}, K={K})")
 
 

@@ -340,7 +340,7 @@ static cudaError_t launch_spmm(cudaStream_t stream, const CUtensorMap& tmap, con
 }
 
 static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws, long long count, int parts,
-                                   const half* bias, int M, int activation)
+                                   const half* bias, int M, int activation, const half* residual)
 {
     const int       threads = 256;
     const long long groups  = (count + 3) / 4;
@@ -357,7 +357,7 @@ static cudaError_t reduce_partials(cudaStream_t stream, half* C, const float* ws
         cfg.attrs                                          = attr;
         cfg.numAttrs                                       = 1;
     }
-    return cudaLaunchKernelEx(&cfg, splitk_reduce_f32_kernel, C, ws, count, parts, bias, M, activation);
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_f32_kernel, C, ws, count, parts, bias, M, activation, residual);
 }
 
 static cudaError_t reduce_workspace(cudaStream_t stream, half* C, const half* ws, long long count, int parts)
@@ -422,6 +422,7 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
                                    int          Split_K,
                                    const half*  bias,
                                    int          activation,
+                                   const half*  residual = nullptr,
                                    FlashLLMComm* comm = nullptr,
                                    int           phases = 3)
 {
@@ -461,6 +462,7 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
     params.status       = st->status;
     params.bias         = bias;
     params.activation   = activation;
+    params.residual     = residual;
     params.M            = M_Global;
     params.N            = N_Global;
     params.K            = K_Global;
@@ -535,12 +537,12 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
         count_launch();
         return cudaLaunchKernelEx(&cfg, allreduce_sum_kernel, C, reinterpret_cast<const float*>(mine + set_slots),
                                   comm->max_elems, reinterpret_cast<const unsigned int*>(mine + set_flags), kCommFlagsPerRank,
-                                  comm->epoch, comm->world, grid_ctas, count, bias, M_Global, activation, st->status,
+                                  comm->epoch, comm->world, grid_ctas, count, bias, M_Global, activation, residual, st->status,
                                   comm->wait_limit_ns);
     }
     if (pl.workspace_k > 1)
         return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k,
-                               bias, M_Global, activation);
+                               bias, M_Global, activation, residual);
     return cudaSuccess;
 }
 
@@ -582,6 +584,29 @@ int FlashLLM_SpMM_SplitK_BiasAct(void*       stream,
                                             TileOffsets, static_cast<const half*>(B), static_cast<half*>(C), M, N, K,
                                             static_cast<half*>(Reduction_Workspace), Split_K,
                                             static_cast<const half*>(bias), activation));
+}
+
+int FlashLLM_SpMM_SplitK_Epilogue(void*       stream,
+                                  const void* Compressed_A,
+                                  const int*  TileOffsets,
+                                  const void* B,
+                                  void*       C,
+                                  int         M,
+                                  int         N,
+                                  int         K,
+                                  void*       Reduction_Workspace,
+                                  int         Split_K,
+                                  const void* bias,
+                                  int         activation,
+                                  const void* residual)
+{
+    if ((activation != kActNone && activation != kActRelu) || (residual != nullptr && residual == C))
+        return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(spmm_launch_all(static_cast<cudaStream_t>(stream), static_cast<const uint4*>(Compressed_A),
+                                            TileOffsets, static_cast<const half*>(B), static_cast<half*>(C), M, N, K,
+                                            static_cast<half*>(Reduction_Workspace), Split_K,
+                                            static_cast<const half*>(bias), activation,
+                                            static_cast<const half*>(residual)));
 }
 
 int FlashLLM_SpMM_SplitK(void*       stream,
@@ -726,14 +751,16 @@ int FlashLLM_SpMM_SplitK_AllReduce(void*       comm,
                                    int         K,
                                    const void* bias,
                                    int         activation,
+                                   const void* residual,
                                    int         phases)
 {
-    if (comm == nullptr || (activation != kActNone && activation != kActRelu) || phases < 1 || phases > 3)
+    if (comm == nullptr || (activation != kActNone && activation != kActRelu) || phases < 1 || phases > 3
+        || (residual != nullptr && residual == C))
         return static_cast<int>(cudaErrorInvalidValue);
     return static_cast<int>(spmm_launch_all(static_cast<cudaStream_t>(stream), static_cast<const uint4*>(Compressed_A),
                                             TileOffsets, static_cast<const half*>(B), static_cast<half*>(C), M, N, K,
                                             nullptr, 1, static_cast<const half*>(bias), activation,
-                                            static_cast<FlashLLMComm*>(comm), phases));
+                                            static_cast<const half*>(residual), static_cast<FlashLLMComm*>(comm), phases));
 }
 
 int FlashLLM_SplitK_Reduction(void* stream, void* C, const void* Reduction_Workspace, int M, int N, int Split_K)

@@ -40,6 +40,7 @@ struct SpmmParams {
     unsigned int* status;        // per-device status word
     const half*   bias;          // [M] added to every output row before the activation, or nullptr
     int           activation;    // kActNone or kActRelu, applied to the fp32 sum before the one fp16 rounding
+    const half*   residual;      // [N][M] like C, added after the activation and before the rounding, or nullptr
     int           M, N, K;
     int           k_tiles;  // K / 64
     SpmmPlan      plan;
@@ -59,16 +60,21 @@ constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
 constexpr int kDepsResolved = 2;
 
 // Output epilogue shared by every place that rounds a finished fp32 sum to fp16: optional bias of output feature m,
-// optional ReLU.  (The reference's callers do this in a separate pass over fp16 C, third_party/ft.patch
-// ParallelGpt FFN: add_bias_relu after the first FFN GEMM; here it costs one add and one max before the rounding.)
+// optional ReLU, optional residual (element `at` of a matrix laid out like C).  (The reference's callers do this in
+// separate passes over fp16 C, third_party/ft.patch ParallelGpt FFN: add_bias_relu after the first FFN GEMM,
+// add_bias_residual after the second and after the attention output projection; here it costs one add each and one
+// max before the rounding.)
 constexpr int kActNone = 0, kActRelu = 1;
 
-__device__ __forceinline__ half finish_output(float acc, const half* bias, int m, int activation)
+__device__ __forceinline__ half finish_output(float acc, const half* bias, int m, int activation, const half* residual,
+                                              size_t at)
 {
     if (bias != nullptr)
         acc += __half2float(bias[m]);
     if (activation == kActRelu)
         acc = fmaxf(acc, 0.0f);
+    if (residual != nullptr)
+        acc += __half2float(residual[at]);
     return __float2half_rn(acc);
 }
 
@@ -339,7 +345,8 @@ __device__ __forceinline__ void accumulators_to_output(const SpmmParams& p, uint
                         else if (part_tile)
                             part_tile[at] = r[i];
                         else
-                            out_tile[at] = finish_output(r[i], p.bias, tile_row * kTileM + row_in_tile, p.activation);
+                            out_tile[at] = finish_output(r[i], p.bias, tile_row * kTileM + row_in_tile, p.activation, p.residual,
+                                                         tile_off + at);
                     }
             }
         }
@@ -379,7 +386,9 @@ __device__ __forceinline__ void cluster_reduce_store(const SpmmParams& p, uint32
             else if (part_tile)
                 part_tile[static_cast<size_t>(n) * p.M + m] = acc;
             else
-                out_tile[static_cast<size_t>(n) * p.M + m] = finish_output(acc, p.bias, tile_row * kTileM + m, p.activation);
+                out_tile[static_cast<size_t>(n) * p.M + m] =
+                    finish_output(acc, p.bias, tile_row * kTileM + m, p.activation, p.residual,
+                                  tile_off + static_cast<size_t>(n) * p.M + m);
         }
     }
 }
@@ -880,7 +889,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
 // Sums the fp32 partial matrices this library parks in the caller's workspace when workspace_k > 1 and rounds once:
 // C[i] = fp16(sum_s ws[s*count + i]); four outputs per thread.
 __global__ void splitk_reduce_f32_kernel(half* __restrict__ C, const float* __restrict__ ws, long long count, int parts,
-                                         const half* __restrict__ bias, int M, int activation)
+                                         const half* __restrict__ bias, int M, int activation,
+                                         const half* __restrict__ residual)
 {
     ptx::grid_launch_dependents();  // the next SpMM may begin streaming its weights
     ptx::grid_dependency_wait();    // the partial matrices come from the SpMM launched just before
@@ -898,10 +908,10 @@ __global__ void splitk_reduce_f32_kernel(half* __restrict__ C, const float* __re
     const int m = static_cast<int>(i4 % M);  // C is [N][M] and M is a multiple of 4: the four share a row of C
     uint2     o;
     half*     oh = reinterpret_cast<half*>(&o);
-    oh[0]        = finish_output(acc.x, bias, m, activation);
-    oh[1]        = finish_output(acc.y, bias, m + 1, activation);
-    oh[2]        = finish_output(acc.z, bias, m + 2, activation);
-    oh[3]        = finish_output(acc.w, bias, m + 3, activation);
+    oh[0]        = finish_output(acc.x, bias, m, activation, residual, static_cast<size_t>(i4));
+    oh[1]        = finish_output(acc.y, bias, m + 1, activation, residual, static_cast<size_t>(i4) + 1);
+    oh[2]        = finish_output(acc.z, bias, m + 2, activation, residual, static_cast<size_t>(i4) + 2);
+    oh[3]        = finish_output(acc.w, bias, m + 3, activation, residual, static_cast<size_t>(i4) + 3);
     *reinterpret_cast<uint2*>(C + i4) = o;
 }
 
@@ -945,7 +955,8 @@ constexpr unsigned kStatusPeerWaitExpired = 32u;  // a GPU of the group did not 
 __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, long long slot_stride,
                                      const unsigned int* flags, int flag_stride, unsigned int epoch, int world,
                                      int flags_per_rank, long long count, const half* __restrict__ bias, int M,
-                                     int activation, unsigned int* status, unsigned long long wait_limit_ns)
+                                     int activation, const half* __restrict__ residual, unsigned int* status,
+                                     unsigned long long wait_limit_ns)
 {
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
@@ -997,10 +1008,10 @@ __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, l
     const int m = static_cast<int>(i4 % M);
     uint2     o;
     half*     oh = reinterpret_cast<half*>(&o);
-    oh[0]        = finish_output(acc.x, bias, m, activation);
-    oh[1]        = finish_output(acc.y, bias, m + 1, activation);
-    oh[2]        = finish_output(acc.z, bias, m + 2, activation);
-    oh[3]        = finish_output(acc.w, bias, m + 3, activation);
+    oh[0]        = finish_output(acc.x, bias, m, activation, residual, static_cast<size_t>(i4));
+    oh[1]        = finish_output(acc.y, bias, m + 1, activation, residual, static_cast<size_t>(i4) + 1);
+    oh[2]        = finish_output(acc.z, bias, m + 2, activation, residual, static_cast<size_t>(i4) + 2);
+    oh[3]        = finish_output(acc.w, bias, m + 3, activation, residual, static_cast<size_t>(i4) + 3);
     *reinterpret_cast<uint2*>(C + i4) = o;
 }
 

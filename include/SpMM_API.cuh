@@ -177,6 +177,24 @@ int FlashLLM_SpMM_SplitK_BiasAct(void*       stream,
                                  const void* bias,
                                  int         activation);
 
+/* The same with the residual of the decoder layer added as well (FasterTransformer's add_bias_residual pass after the
+ * attention output projection and after the second FFN GEMM, third_party/ft.patch FfnLayer / ParallelGpt call sites):
+ * C[n][m] = fp16(act(sum + bias[m]) + residual[n][m]).  `residual` is a device matrix laid out like C that does not
+ * overlap it, or nullptr (then identical to FlashLLM_SpMM_SplitK_BiasAct). */
+int FlashLLM_SpMM_SplitK_Epilogue(void*       stream,
+                                  const void* Compressed_A,
+                                  const int*  TileOffsets,
+                                  const void* B,
+                                  void*       C,
+                                  int         M,
+                                  int         N,
+                                  int         K,
+                                  void*       Reduction_Workspace,
+                                  int         Split_K,
+                                  const void* bias,
+                                  int         activation,
+                                  const void* residual);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Row-parallel SpMM with the all-reduce fused in (tensor-parallel inference: the attention output projection and
  * the second feed-forward matmul hold a slice of K on every GPU, so every GPU's product is a partial sum).  The
@@ -209,8 +227,9 @@ int FlashLLM_Comm_Destroy(void* comm);
  * wait for a partner that never comes. */
 int FlashLLM_Comm_SetWaitLimit(void* comm, int milliseconds);
 
-/* C[n][m] = act(sum over the group's GPUs w of sum_k A_w[m][k] * B_w[n][k] + bias[m]) on every GPU.  Arguments as
- * FlashLLM_SpMM_SplitK_BiasAct without workspace and Split_K (the K cut of one GPU's product stays inside thread-block
+/* C[n][m] = act(sum over the group's GPUs w of sum_k A_w[m][k] * B_w[n][k] + bias[m]) + residual[n][m] on every GPU
+ * (`residual`: this GPU's copy of the layer input, or nullptr).  Arguments as FlashLLM_SpMM_SplitK_Epilogue without
+ * workspace and Split_K (the K cut of one GPU's product stays inside thread-block
  * clusters).  `phases`: 3 = both kernels (the normal call); 1 = the SpMM and its stores only, 2 = the summing kernel
  * only -- for a host that drives several GPUs' calls from one thread and wants all sends enqueued before any sum. */
 int FlashLLM_SpMM_SplitK_AllReduce(void*       comm,
@@ -224,6 +243,7 @@ int FlashLLM_SpMM_SplitK_AllReduce(void*       comm,
                                    int         K,
                                    const void* bias,
                                    int         activation,
+                                   const void* residual,
                                    int         phases);
 
 /* SpMM for callers that must not allocate device memory.  (No counterpart in the reference, whose callers always

@@ -53,6 +53,33 @@ def test_fused_allreduce_matches_the_unsharded_product(lib, oracle, M, K_full, N
         group.close()
 
 
+def test_fused_allreduce_adds_the_residual_once(lib, oracle):
+    """The decoder layer's residual goes in after the group's sum and before the one rounding, on every rank."""
+    from flash_llm_b200 import tp_chain
+    M, K_full, N, world = 768, 3072, 16, 4
+    A, B, parts, k = _shards(lib, M, K_full, N, world, seed=91)
+    bias = lib.synthetic.dense_uniform_matrix(1, M, 92).reshape(M)
+    residual = lib.synthetic.dense_uniform_matrix(N, M, 93)
+    want = oracle.gemm_f32(A, B) + bias.numpy().astype(np.float32)[None, :] + residual.numpy().astype(np.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    group = tp_chain.LocalGroup(lib, world, M * N)
+    bias_d, residual_d = bias.cuda(), residual.cuda()
+    try:
+        outs = [torch.empty((N, M), dtype=torch.float16, device="cuda") for _ in range(world)]
+        for phase in (1, 2):
+            for r, (comp, offs, B_r) in enumerate(parts):
+                lib.spmm_splitk_allreduce(group.comms[r], stream, comp.data_ptr(), offs.data_ptr(), B_r.data_ptr(),
+                                          outs[r].data_ptr(), M, N, k, bias=bias_d.data_ptr(),
+                                          residual=residual_d.data_ptr(), phases=phase)
+        torch.cuda.synchronize()
+        assert lib.consume_status() == 0
+        assert_close(outs[0].cpu().numpy(), want, "bias + residual on the summed product")
+        for r in range(1, world):
+            assert torch.equal(outs[r], outs[0])
+    finally:
+        group.close()
+
+
 def test_fused_allreduce_applies_bias_and_relu_after_the_sum(lib, oracle):
     from flash_llm_b200 import tp_chain
     M, K_full, N, world = 512, 2048, 16, 2
@@ -107,11 +134,11 @@ def test_fused_allreduce_argument_checks(lib):
     from flash_llm_b200 import tp_chain
     L = lib.library()
     fake = 0x1000
-    assert L.FlashLLM_SpMM_SplitK_AllReduce(None, None, fake, fake, fake, fake, 256, 16, 256, None, 0, 3) == 1  # no comm
+    assert L.FlashLLM_SpMM_SplitK_AllReduce(None, None, fake, fake, fake, fake, 256, 16, 256, None, 0, None, 3) == 1  # no comm
     group = tp_chain.LocalGroup(lib, 2, 256 * 16)
     try:
         # output larger than the communicator was sized for
-        assert L.FlashLLM_SpMM_SplitK_AllReduce(group.comms[0], None, fake, fake, fake, fake, 512, 16, 256, None, 0, 3) == 1
-        assert L.FlashLLM_SpMM_SplitK_AllReduce(group.comms[0], None, fake, fake, fake, fake, 256, 16, 256, None, 0, 4) == 1
+        assert L.FlashLLM_SpMM_SplitK_AllReduce(group.comms[0], None, fake, fake, fake, fake, 512, 16, 256, None, 0, None, 3) == 1
+        assert L.FlashLLM_SpMM_SplitK_AllReduce(group.comms[0], None, fake, fake, fake, fake, 256, 16, 256, None, 0, None, 4) == 1
     finally:
         group.close()
