@@ -353,8 +353,9 @@ def set_launch_overlap(enable: bool) -> None:
 
 
 PLAN_FIELDS = ("cluster_k", "workspace_k", "a_stages", "b_stages", "b_batch", "ring_slots", "chunk_vectors",
-               "scatter_warps", "producers", "path")
+               "scatter_warps", "producers", "path", "reduce")
 PATH_RING, PATH_DIRECT = 1, 2
+REDUCE_SECOND_KERNEL, REDUCE_LAST_CTA = 1, 2
 
 
 def set_plan(**fields: int) -> None:

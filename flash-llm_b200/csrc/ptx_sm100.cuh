@@ -15,6 +15,22 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p)
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Flag traffic between GPUs: an acquire load at system scope (what it returns, and everything the writer did before
+// its release, is visible to the loads that follow) and the matching release store.
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const unsigned int* ptr)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const unsigned int* ptr)
+{
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns()
 {
     uint64_t t;

@@ -27,6 +27,13 @@ __device__ unsigned int g_status_word = 0;
 constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
+// Arrival counters of the in-kernel split-K sum: kCounterSets sets of one word per output tile, all zero between
+// launches.  Launches of one stream are ordered (the sum of one is over before the next one's B loader is let
+// through), so a set is bound to a stream; calls on other streams take other sets, and a call that finds no free
+// set, or has more output tiles than a set holds, sums with the second kernel instead.
+constexpr int kCounterSets = 32, kCounterTiles = 2048;
+static __device__ unsigned int g_tile_counters[kCounterSets * kCounterTiles];
+
 static std::atomic<unsigned long long> g_launches{0};
 
 void count_launch()
@@ -45,7 +52,23 @@ struct DeviceState {
     int            smem_optin = 0;
     unsigned int*  status     = nullptr;
     unsigned char* noalloc_scratch = nullptr;  // device address of g_noalloc_scratch on this device
+    unsigned int*  tile_counters   = nullptr;  // device address of g_tile_counters on this device
+    int            counter_streams = 0;        // streams that own a counter set so far
+    cudaStream_t   counter_stream[kCounterSets] = {nullptr};
 };
+
+// The counter set of `stream` on this device, or nullptr when all sets are taken by other streams.
+static unsigned int* counters_of_stream(DeviceState* st, cudaStream_t stream)
+{
+    std::lock_guard<std::mutex> lock(st->mutex);
+    for (int i = 0; i < st->counter_streams; ++i)
+        if (st->counter_stream[i] == stream)
+            return st->tile_counters + static_cast<size_t>(i) * kCounterTiles;
+    if (st->counter_streams >= kCounterSets)
+        return nullptr;
+    st->counter_stream[st->counter_streams] = stream;
+    return st->tile_counters + static_cast<size_t>(st->counter_streams++) * kCounterTiles;
+}
 
 static DeviceState g_devices[kMaxDevices];
 
@@ -121,6 +144,8 @@ static DeviceState* device_state(cudaError_t* err)
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->status), g_status_word);
     if (e == cudaSuccess)
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->noalloc_scratch), g_noalloc_scratch);
+    if (e == cudaSuccess)
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st->tile_counters), g_tile_counters);
     // The opt-in limit is a per-device property of each kernel; raise it once instead of on every call
     // (the reference calls cudaFuncSetAttribute per launch, csrc/SpMM_API.cu:36-37).
     if (e == cudaSuccess)
@@ -190,7 +215,9 @@ static bool is_pow2(int v)
 // Chooses how to cut K and how deep to pipeline.  Takes the place of the reference's per-N switch over
 // TilingConfig instances (csrc/SpMM_API.cu:79-118) and of its hand-tuned Split_K tables
 // (kernel_benchmark/benchmark.sh:13-15).
-static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Split_K, SpmmPlan* out)
+// `max_parts`: workspace parts the caller has room for (Split_K / 2 for a caller's Reduction_Workspace, whose Split_K
+// fp16 matrices hold half as many fp32 ones).
+static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int max_parts, SpmmPlan* out)
 {
     PlanOverride ov;
     {
@@ -231,52 +258,61 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
         pl.chunk_vectors = 0;
     }
     // How to cut K.  A CTA that owns a whole tile row needs no reduction and pays its set-up and pipeline fill once,
-    // so K is cut only to fill the GPU.  With `slots` CTAs resident at a time, G workspace parts per tile row run in
-    // ceil(rows*G/slots) waves of CTAs that each process k_tiles/G tiles after a fixed cost worth about 16 tiles, and
-    // the second kernel adds about half a tile's time per part; the G with the smallest total wins.  (Fitted to
-    // measurements: 216 tile rows on 296 slots gain nothing from 2 or 3 parts and 8 % from 4; 9 tile rows of 576
-    // K tiles run 39 / 25 / 23 us with 8 / 16 / 32 parts.)  Parts that go through the caller's workspace (fp32 partial
-    // matrices; at most Split_K/2 of them) are cheaper than parts of a thread-block cluster (summed through
-    // distributed shared memory, CTAs co-scheduled) except on small problems, where the second launch costs more
-    // than it saves; clusters also take what the workspace cannot.  Replaces the reference's hand-tuned Split_K
-    // tables (kernel_benchmark/benchmark.sh:13-15).
-    const int slots     = st->sm_count * (two_per_sm ? ((direct && pl.producers == 1) ? kDirectBlocks : 2) : 1);
-    const int max_extra = ((static_cast<long long>(M) * N) % 4 != 0) ? 1 : (Split_K / 2 > 1 ? Split_K / 2 : 1);
-    // (with launch overlap on, the second kernel hides behind its neighbours and workspace parts win at every size)
-    const bool small    = static_cast<long long>(tile_rows) * k_tiles <= 4096
-                       && g_launch_overlap.load(std::memory_order_relaxed) == 0;
-    int        best_s = 1, best_g = 1;
-    if (!small) {
-        double best_cost = 0.0;
-        for (int g = 1; g <= max_extra && g <= 32 && g <= k_tiles; ++g) {
-            const long long ctas  = static_cast<long long>(ctas_flat) * g;
-            const double    waves = static_cast<double>((ctas + slots - 1) / slots);
-            const double    cost  = waves * (static_cast<double>((k_tiles + g - 1) / g) + 16.0) + (g > 1 ? 0.5 * g : 0.0);
-            if (g == 1 || cost < best_cost) {
+    // so K is cut only to fill the GPU.  S parts are summed inside a thread-block cluster (distributed shared memory),
+    // G parts through fp32 partial tiles in the workspace (summed by the last CTA of a tile to finish, or by a second
+    // kernel).  A launch of rows*G clusters of S CTAs runs in ceil(rows*G / capacity(S)) waves, where capacity(S) is
+    // the number of clusters of S CTAs the GPU holds at a time -- measured, and well below slots/S for S >= 3 (71
+    // clusters of 4, 33 of 8 on 296 slots): one cluster more than that and the launch takes twice as long.  Every
+    // CTA processes k_tiles/(S*G) tiles after a fixed cost worth about 16 tiles; a cluster sum costs about 3 more,
+    // the sum by the last CTA 2 + 0.1 per part, a second kernel half a tile per part.  The cheapest (S, G) wins,
+    // fewer parts on a tie.  Replaces the reference's hand-tuned Split_K tables (kernel_benchmark/benchmark.sh:13-15).
+    static const int kClustersResident2[kMaxClusterK + 1] = {0, 296, 148, 92, 71, 56, 45, 37, 33};  // two CTAs per SM
+    static const int kClustersResident1[kMaxClusterK + 1] = {0, 148, 74, 45, 33, 26, 22, 15, 15};   // one CTA per SM
+    const bool two_resident = two_per_sm && ((direct && pl.producers == 1) ? kDirectBlocks : 2) == 2;
+    const int* resident     = two_resident ? kClustersResident2 : kClustersResident1;
+    auto capacity = [&](int S_) {  // the table is for 148 SMs
+        const long long c = static_cast<long long>(resident[S_]) * st->sm_count / 148;
+        return c < 1 ? 1ll : c;
+    };
+    const int max_extra = max_parts > 1 ? max_parts : 1;
+    // (measured on eleven shapes from 9216x1152 to 9216x36864: with launch overlap the second kernel hides behind its
+    // neighbours and beats the sum by the last CTA, which sits on every tile's critical path, by ~2 us per call;
+    // without overlap the two are level.  The fused all-reduce always sums by the last CTA: that CTA also sends.)
+    pl.reduce           = ov.v[kPlanReduce] ? ov.v[kPlanReduce] : kReduceSecondKernel;
+    if (ctas_flat > kCounterTiles)
+        pl.reduce = kReduceSecondKernel;
+    // (without launch overlap a second kernel costs a whole launch: small problems then do better with clusters alone)
+    const bool no_second = pl.reduce == kReduceSecondKernel && static_cast<long long>(tile_rows) * k_tiles <= 4096
+                           && g_launch_overlap.load(std::memory_order_relaxed) == 0;
+    int    best_s = 1, best_g = 1;
+    double best_cost = 0.0;
+    for (int s_ = 1; s_ <= kMaxClusterK && s_ <= k_tiles; ++s_) {
+        for (int g = 1; g <= max_extra && g <= 32 && s_ * g <= k_tiles; ++g) {
+            if (g > 1 && no_second)
+                break;
+            const long long clusters = static_cast<long long>(ctas_flat) * g;
+            const double    waves    = static_cast<double>((clusters + capacity(s_) - 1) / capacity(s_));
+            const double    per_cta  = static_cast<double>((k_tiles + s_ * g - 1) / (s_ * g)) + 16.0 + (s_ > 1 ? 3.0 : 0.0)
+                                    + (g > 1 && pl.reduce == kReduceLastCta ? 2.0 + 0.1 * g : 0.0);
+            const double cost = waves * per_cta + (g > 1 && pl.reduce == kReduceSecondKernel ? 0.5 * g : 0.0);
+            if ((s_ == 1 && g == 1) || cost < best_cost - 1e-9
+                || (cost < best_cost + 1e-9 && s_ * g < best_s * best_g)) {
                 best_cost = cost;
+                best_s    = s_;
                 best_g    = g;
             }
         }
-    }
-    if (static_cast<long long>(ctas_flat) * best_g * 10 < static_cast<long long>(slots) * 6) {
-        best_s = slots / (ctas_flat * best_g);
-        if (best_s < 1)
-            best_s = 1;
-        if (best_s > kMaxClusterK)
-            best_s = kMaxClusterK;
     }
     pl.cluster_k = ov.v[kPlanClusterK] ? ov.v[kPlanClusterK] : best_s;
     if (pl.cluster_k > k_tiles)
         pl.cluster_k = k_tiles;
     int extra = ov.v[kPlanWorkspaceK] ? ov.v[kPlanWorkspaceK] : best_g;
-    if (extra > Split_K / 2)
-        extra = Split_K / 2;  // the workspace is promised to hold Split_K fp16 matrices = Split_K/2 fp32 partials
+    if (extra > max_extra)
+        extra = max_extra;  // the workspace is promised to hold Split_K fp16 matrices = Split_K/2 fp32 partials
     if (extra * pl.cluster_k > k_tiles)
         extra = k_tiles / pl.cluster_k;
     if (extra < 1)
         extra = 1;
-    if ((static_cast<long long>(M) * N) % 4 != 0)
-        extra = 1;  // the workspace reduction moves four values per thread
     pl.workspace_k = extra;
     // room for this CTA's slice of TileOffsets (K tiles of the longest part, plus one), up to 8 KB
     const int longest = (k_tiles + pl.cluster_k * pl.workspace_k - 1) / (pl.cluster_k * pl.workspace_k) + 1;
@@ -296,7 +332,8 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int Spl
     const bool ok = (pl.path == kPathRing || pl.path == kPathDirect) && (direct ? direct_ok : ring_ok)
                     && pl.a_stages >= 1 && pl.a_stages <= kMaxAStages && pl.b_stages >= 1 && pl.b_stages <= kMaxBStages
                     && pl.b_batch >= 1 && pl.b_batch <= 256 && pl.cluster_k >= 1 && pl.cluster_k <= kMaxClusterK
-                    && pl.workspace_k >= 1 && pl.smem_bytes <= st->smem_optin
+                    && pl.workspace_k >= 1 && (pl.reduce == kReduceSecondKernel || pl.reduce == kReduceLastCta)
+                    && pl.smem_bytes <= st->smem_optin
                     // the fp32 partial tile of the cluster reduction is parked over the pipeline buffers
                     && pl.smem_bytes - 1024 - 4 * pl.offsets_staged >= pl.n_tile * kTileM * 4;
     if (!ok)
@@ -382,7 +419,7 @@ using namespace flashllm;
 
 // Receive buffers of a GPU group for the fused row-parallel SpMM + all-reduce.  Every GPU owns one buffer with two
 // sets (used by alternate calls) of `world` fp32 slots [max_elems] and `world` x kCommFlagsPerRank flag words:
-//   [set 0 slots][set 1 slots][set 0 flags][set 1 flags]
+//   [set 0 slots][set 1 slots][set 0 flags][set 1 flags][own partial matrices][own arrival counters]
 // Slot w / flag row w of a GPU's buffer is written only by GPU w.  While one call's sums are still being read on a
 // slow GPU, a fast GPU's next call writes the other set; it cannot start the call after that before the slow GPU has
 // taken part in the next one, so two sets are enough.
@@ -404,9 +441,19 @@ static size_t comm_slot_bytes(int world, long long max_elems)
     return static_cast<size_t>(world) * static_cast<size_t>(max_elems) * sizeof(float);
 }
 
+static size_t comm_flag_bytes(int world)
+{
+    return static_cast<size_t>(world) * kCommFlagsPerRank * sizeof(unsigned int);
+}
+
+// ... followed by what only the owning GPU touches: room for kCommLocalParts fp32 partial matrices of its own K
+// split, and the arrival counters of that split's in-kernel sum (zero between calls).
+constexpr int kCommLocalParts = 8, kCommCounterTiles = 4096;
+
 static size_t comm_buffer_bytes(int world, long long max_elems)
 {
-    return 2 * comm_slot_bytes(world, max_elems) + 2 * static_cast<size_t>(world) * kCommFlagsPerRank * sizeof(unsigned int);
+    return 2 * comm_slot_bytes(world, max_elems) + 2 * comm_flag_bytes(world)
+           + kCommLocalParts * static_cast<size_t>(max_elems) * sizeof(float) + kCommCounterTiles * sizeof(unsigned int);
 }
 
 // SpMM_SplitK_API plus the output epilogue (bias of output feature m, activation) the public entry points select.
@@ -444,14 +491,12 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
         return err;
 
     SpmmParams params{};
-    if ((err = make_plan(st, M_Global, N_Global, K_Global, comm ? 1 : Split_K, &params.plan)) != cudaSuccess)
+    if ((err = make_plan(st, M_Global, N_Global, K_Global, comm ? kCommLocalParts : Split_K / 2, &params.plan))
+        != cudaSuccess)
         return err;
     SpmmPlan& pl = params.plan;
-    if (comm && pl.workspace_k != 1)
-        return cudaErrorInvalidConfiguration;  // a pinned plan asked for workspace parts: partial sums must leave the
-                                               // kernel complete to be pushed
-    // The partial-matrix pass reads 16-byte groups of the workspace and writes 8-byte groups of C.
-    if (pl.workspace_k > 1
+    // The sum over workspace parts reads 16-byte groups of the workspace and writes 8-byte groups of C.
+    if (!comm && pl.workspace_k > 1
         && ((reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u) != 0 || (reinterpret_cast<uintptr_t>(C) & 7u) != 0))
         pl.workspace_k = 1;
 
@@ -459,6 +504,11 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
     params.tile_offsets = TileOffsets;
     params.out          = C;
     params.partial      = pl.workspace_k > 1 ? reinterpret_cast<float*>(Reduction_Workspace) : nullptr;
+    if (!comm && pl.workspace_k > 1 && pl.reduce == kReduceLastCta) {
+        params.tile_counters = counters_of_stream(st, stream);
+        if (params.tile_counters == nullptr)
+            pl.reduce = kReduceSecondKernel;  // every counter set belongs to another stream
+    }
     params.status       = st->status;
     params.bias         = bias;
     params.activation   = activation;
@@ -486,18 +536,28 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
     const int tile_rows = M_Global / kTileM;
     const int n_tiles   = (N_Global + pl.n_tile - 1) / pl.n_tile;
     const int grid_ctas = pl.cluster_k * tile_rows * n_tiles * pl.workspace_k;
+    // flags a sender raises per call: one per CTA, or one per output tile when the last CTA of a tile sends its sum
+    const int comm_flags = pl.workspace_k > 1 ? tile_rows * n_tiles : grid_ctas;
     size_t    set_slots = 0, set_flags = 0;
     if (comm) {
         const long long elems = static_cast<long long>(M_Global) * N_Global;
-        if (elems > comm->max_elems || elems % 4 != 0 || grid_ctas > kCommFlagsPerRank
-            || (reinterpret_cast<uintptr_t>(C) & 7u) != 0)
+        if (elems > comm->max_elems || elems % 4 != 0 || comm_flags > kCommFlagsPerRank
+            || (pl.workspace_k > 1 && tile_rows * n_tiles > kCommCounterTiles) || (reinterpret_cast<uintptr_t>(C) & 7u) != 0)
             return cudaErrorInvalidValue;
+        if (pl.workspace_k > 1) {  // own K split: parts parked in the own buffer, summed and sent by the last CTA
+            unsigned char* own   = comm->buffer[comm->rank] + 2 * comm_slot_bytes(comm->world, comm->max_elems)
+                                 + 2 * comm_flag_bytes(comm->world);
+            pl.reduce            = kReduceLastCta;
+            params.partial       = reinterpret_cast<float*>(own);
+            params.tile_counters = reinterpret_cast<unsigned int*>(own + kCommLocalParts * static_cast<size_t>(comm->max_elems)
+                                                                                 * sizeof(float));
+        }
         if (phases & 1)
             comm->epoch += 1;  // a new call; a sum-only call belongs to the call whose stores went out last
         const int set       = static_cast<int>(comm->epoch & 1u);
         set_slots           = static_cast<size_t>(set) * comm_slot_bytes(comm->world, comm->max_elems);
         set_flags           = 2 * comm_slot_bytes(comm->world, comm->max_elems)
-                    + static_cast<size_t>(set) * comm->world * kCommFlagsPerRank * sizeof(unsigned int);
+                    + static_cast<size_t>(set) * comm_flag_bytes(comm->world);
         params.push_world   = comm->world;
         params.push_epoch   = comm->epoch;
         for (int w = 0; w < comm->world; ++w) {
@@ -537,10 +597,10 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
         count_launch();
         return cudaLaunchKernelEx(&cfg, allreduce_sum_kernel, C, reinterpret_cast<const float*>(mine + set_slots),
                                   comm->max_elems, reinterpret_cast<const unsigned int*>(mine + set_flags), kCommFlagsPerRank,
-                                  comm->epoch, comm->world, grid_ctas, count, bias, M_Global, activation, residual, st->status,
-                                  comm->wait_limit_ns);
+                                  comm->epoch, comm->world, comm_flags, count, bias, M_Global, activation, residual, st->status,
+                                  comm->wait_limit_ns, phases == 3 ? 0 : 1);
     }
-    if (pl.workspace_k > 1)
+    if (pl.workspace_k > 1 && pl.reduce == kReduceSecondKernel)
         return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k,
                                bias, M_Global, activation, residual);
     return cudaSuccess;
@@ -794,11 +854,11 @@ int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count)
     if (!st)
         return static_cast<int>(err);
     SpmmPlan pl{};
-    if ((err = make_plan(st, M, N, K, Split_K, &pl)) != cudaSuccess)
+    if ((err = make_plan(st, M, N, K, Split_K / 2, &pl)) != cudaSuccess)
         return static_cast<int>(err);
     const int values[kPlanFieldCount + 1] = {pl.cluster_k,  pl.workspace_k,   pl.a_stages,      pl.b_stages,  pl.b_batch,
                                              pl.ring_slots, pl.chunk_vectors, pl.scatter_warps, pl.producers, pl.path,
-                                             pl.smem_bytes};
+                                             pl.reduce,     pl.smem_bytes};
     for (int i = 0; i < count && i <= kPlanFieldCount; ++i)
         out[i] = values[i];
     return 0;

@@ -494,7 +494,7 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
         __syncwarp();
         ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     }
-    push_raise_flags(p, *abort_flag == 0u);
+    finish_tile<N_TILE>(p, S, G, n_idx, tile_row, abort_flag);
     if (threadIdx.x == 0)
         FL_CTA_TIME(3);
     if (warp == mma_warp) {

@@ -47,6 +47,10 @@ struct SpmmParams {
     // Fused all-reduce of a row-parallel SpMM (push_world > 0): every finished fp32 value of this GPU's partial product
     // is stored into the receive slot this rank owns on every GPU of the group (its own included) instead of C, and
     // each CTA then raises one flag per GPU; allreduce_sum_kernel on each GPU adds the slots up.
+    // Split-K sum without a second kernel (workspace_k > 1 and tile_counters != nullptr): every CTA stores its fp32
+    // partial tile, then counts itself in on the tile's counter; the CTA that finds all the others already counted adds
+    // the parts up in part order and finishes the output.  Nobody waits.  Counters are zero between launches.
+    unsigned int* tile_counters;
     int           push_world;
     unsigned int  push_epoch;                  // value the flags are raised to by this call
     float*        push_slot[kMaxPushWorld];    // [N][M] fp32 slot of this rank in GPU w's receive buffer
@@ -338,12 +342,12 @@ __device__ __forceinline__ void accumulators_to_output(const SpmmParams& p, uint
                 for (int i = 0; i < 8; ++i)
                     if (c0 + i < n_valid) {
                         const size_t at = static_cast<size_t>(c0 + i) * p.M + row_in_tile;
-                        if (p.push_world > 0) {
+                        if (part_tile)
+                            part_tile[at] = r[i];
+                        else if (p.push_world > 0) {
                             for (int w = 0; w < p.push_world; ++w)
                                 p.push_slot[w][tile_off + at] = r[i];
                         }
-                        else if (part_tile)
-                            part_tile[at] = r[i];
                         else
                             out_tile[at] = finish_output(r[i], p.bias, tile_row * kTileM + row_in_tile, p.activation, p.residual,
                                                          tile_off + at);
@@ -356,6 +360,8 @@ __device__ __forceinline__ void accumulators_to_output(const SpmmParams& p, uint
                 red[(c0 + i) * kTileM + row_in_tile] = r[i];
         }
     }
+    if (S == 1 && part_tile != nullptr && p.tile_counters != nullptr)
+        __threadfence();  // this thread's partial sums are visible device-wide before the CTA counts itself in
 }
 
 // Between the two cluster barriers: every CTA of the cluster has parked its fp32 partial tile [N_TILE][128] at `base`
@@ -379,34 +385,115 @@ __device__ __forceinline__ void cluster_reduce_store(const SpmmParams& p, uint32
         for (int q = 0; q < S; ++q)
             acc += ptx::ld_dsmem_f32(ptx::map_to_rank(base + static_cast<uint32_t>(e) * 4u, q));
         if (store_ok) {
-            if (p.push_world > 0) {
+            if (part_tile)
+                part_tile[static_cast<size_t>(n) * p.M + m] = acc;
+            else if (p.push_world > 0) {
                 for (int w = 0; w < p.push_world; ++w)
                     p.push_slot[w][tile_off + static_cast<size_t>(n) * p.M + m] = acc;
             }
-            else if (part_tile)
-                part_tile[static_cast<size_t>(n) * p.M + m] = acc;
             else
                 out_tile[static_cast<size_t>(n) * p.M + m] =
                     finish_output(acc, p.bias, tile_row * kTileM + m, p.activation, p.residual,
                                   tile_off + static_cast<size_t>(n) * p.M + m);
         }
     }
+    if (part_tile != nullptr && p.tile_counters != nullptr)
+        __threadfence();
 }
 
 // Fused all-reduce, sending side: called by every thread of a CTA after its last store of partial sums.  The barrier
-// orders the CTA's stores before thread 0's system-scope fence, after which the flag of this CTA is raised on every GPU
-// of the group.  Plain peer stores only.
-__device__ __forceinline__ void push_raise_flags(const SpmmParams& p, bool cta_ok)
+// orders the CTA's stores before thread 0's system-scope fence, after which flag `index` of this rank is raised on
+// every GPU of the group.  Plain peer stores only.
+__device__ __forceinline__ void push_raise_flag(const SpmmParams& p, unsigned int index, bool cta_ok)
 {
     if (p.push_world <= 0)
         return;
     __syncthreads();
     if (threadIdx.x == 0 && cta_ok) {  // a CTA that gave up raises nothing: the receivers' waits run out and say so
         __threadfence_system();
-        const unsigned int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
         for (int w = 0; w < p.push_world; ++w)
-            *reinterpret_cast<volatile unsigned int*>(p.push_flag[w] + cta) = p.push_epoch;
+            *reinterpret_cast<volatile unsigned int*>(p.push_flag[w] + index) = p.push_epoch;
     }
+}
+
+// One flag per CTA of the grid (every CTA stored a piece of the output).
+__device__ __forceinline__ void push_raise_flags(const SpmmParams& p, bool cta_ok)
+{
+    push_raise_flag(p, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, cta_ok);
+}
+
+// Word, counted from a CTA's abort flag, that tells its threads whether the CTA is the last of its output tile.
+constexpr int kLastOfTile = 1;
+
+// Split-K sum inside the SpMM kernel.  Called by every thread of every CTA after a __syncthreads() that follows the
+// CTA's stores of its part of the fp32 partial tile (each storing thread has fenced).  The CTA counts itself in on the
+// counter of its output tile; the one that completes the count (`arrivals` = CTAs per output tile) adds the
+// workspace parts in part order -- so the result does not depend on which CTA came last -- applies the epilogue and
+// stores C, or, in a fused all-reduce, stores the sum into every GPU's receive slot and raises the tile's flag.  The
+// counter is back at zero when the launch ends.  No CTA waits for another.
+template<int N_TILE>
+__device__ __forceinline__ void splitk_sum_by_last_cta(const SpmmParams& p, int arrivals, int G, int n_idx, int tile_row,
+                                                       volatile uint32_t* abort_flag)
+{
+    const unsigned int tile_id = static_cast<unsigned int>(n_idx) * gridDim.y + tile_row;
+    if (threadIdx.x == 0) {
+        // arrivals in the low half of the counter; a CTA that gave up also marks the high half, so that the last one
+        // knows the tile's sum is not to be trusted
+        const unsigned int mine = *abort_flag == 0u ? 1u : 0x10001u;
+        __threadfence();
+        const unsigned int before = atomicAdd(p.tile_counters + tile_id, mine);
+        const bool         last   = (before & 0xFFFFu) + 1u == static_cast<unsigned int>(arrivals);
+        if (last)
+            atomicExch(p.tile_counters + tile_id, 0u);  // nobody else touches it again in this launch
+        abort_flag[kLastOfTile] = last ? (((before + mine) >> 16) != 0u ? 2u : 1u) : 0u;
+    }
+    __syncthreads();
+    const unsigned int role = abort_flag[kLastOfTile];
+    if (role == 0u)
+        return;
+    __threadfence();  // the other CTAs' partial sums, stored before they counted themselves in, are visible from here on
+    const int    n_valid  = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
+    const size_t tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
+    const size_t count    = static_cast<size_t>(p.M) * p.N;
+    for (int q = threadIdx.x; q < n_valid * (kTileM / 4); q += blockDim.x) {
+        const int    n  = q / (kTileM / 4), m = (q % (kTileM / 4)) * 4;
+        const size_t at = tile_off + static_cast<size_t>(n) * p.M + m;
+        float4       acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int g = 0; g < G; ++g) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(g) * count + at));
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        if (p.push_world > 0) {
+            for (int w = 0; w < p.push_world; ++w)
+                *reinterpret_cast<float4*>(p.push_slot[w] + at) = acc;
+        }
+        else {
+            const int row = tile_row * kTileM + m;
+            uint2     o;
+            half*     oh = reinterpret_cast<half*>(&o);
+            oh[0]        = finish_output(acc.x, p.bias, row, p.activation, p.residual, at);
+            oh[1]        = finish_output(acc.y, p.bias, row + 1, p.activation, p.residual, at + 1);
+            oh[2]        = finish_output(acc.z, p.bias, row + 2, p.activation, p.residual, at + 2);
+            oh[3]        = finish_output(acc.w, p.bias, row + 3, p.activation, p.residual, at + 3);
+            *reinterpret_cast<uint2*>(p.out + at) = o;
+        }
+    }
+    push_raise_flag(p, tile_id, role == 1u);  // a tile with a part missing raises nothing: the receivers' waits say so
+}
+
+// What every CTA does after its part of the output has left it: the in-kernel split-K sum, or its flag of a fused
+// all-reduce whose partial sums went straight to the receive slots.
+template<int N_TILE>
+__device__ __forceinline__ void finish_tile(const SpmmParams& p, int S, int G, int n_idx, int tile_row,
+                                            volatile uint32_t* abort_flag)
+{
+    if (G > 1 && p.tile_counters != nullptr)
+        splitk_sum_by_last_cta<N_TILE>(p, S * G, G, n_idx, tile_row, abort_flag);
+    else
+        push_raise_flags(p, *abort_flag == 0u);
 }
 
 // smem[stage + 2*loc] = value, for one tiled-CSL word (value in the low half, location in the high half).
@@ -874,7 +961,7 @@ __global__ void __launch_bounds__(kMaxThreads, 1)
         __syncwarp();
         ptx::cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
     }
-    push_raise_flags(p, *abort_flag == 0u);
+    finish_tile<N_TILE>(p, S, G, n_idx, tile_row, abort_flag);
     if (warp == mma_warp) {
         __syncwarp();
         ptx::tmem_dealloc(tmem_acc, kTmemCols);
@@ -948,18 +1035,36 @@ constexpr unsigned kStatusPeerWaitExpired = 32u;  // a GPU of the group did not 
 
 // Fused all-reduce, receiving side: C = fp16(act(sum over the group's GPUs of their fp32 partial products + bias)).
 // `slots` holds `world` matrices [N][M] fp32, `slot_stride` floats apart (slot w written by GPU w); `flags` holds, for
-// each sender, `flag_stride` words of which the first `flags_per_rank` are in use (one per CTA of the sending grid).
-// Before a CTA reads anything it waits, for at most `wait_limit_ns`, until every flag of every sender has reached `epoch` (a sender raises
-// a flag after the stores of one CTA, so all of them together cover the whole matrix).  Slots are added in rank order
-// on every GPU, so all GPUs get the same bits.
+// each sender, `flag_stride` words of which the first `flags_per_rank` are in use (one per CTA or per output tile of
+// the sending grid).  Before a CTA reads anything it waits, for at most `wait_limit_ns`, until every flag of every
+// sender has reached `epoch` (a sender raises a flag after the stores it stands for, so all of them together cover the
+// whole matrix).  Slots are added in rank order on every GPU, so all GPUs get the same bits.
+// `stream_ordered` != 0: the kernel first waits for everything enqueued before it on its stream (needed when the
+// senders are kernels of the same stream on the same GPU: nothing else guarantees that they run at all while this
+// one polls).  With 0 the flags are the only dependency: this GPU's sender is the launch right before, all of whose
+// CTAs are resident or finished by the time a dependent launch starts, and the other senders run on other GPUs; the
+// kernel then neither waits for its predecessor to drain nor for its peer stores to be flushed.
 __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, long long slot_stride,
                                      const unsigned int* flags, int flag_stride, unsigned int epoch, int world,
                                      int flags_per_rank, long long count, const half* __restrict__ bias, int M,
                                      int activation, const half* __restrict__ residual, unsigned int* status,
-                                     unsigned long long wait_limit_ns)
+                                     unsigned long long wait_limit_ns, int stream_ordered)
 {
+#ifdef FLASHLLM_CTA_TIMES
+#define FL_SUM_TIME(slot)                                                                                               \
+    do {                                                                                                               \
+        if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))                                      \
+            g_cta_times[4u * (4000u + (blockIdx.x == 0 ? 0u : 1u)) + (slot)] = ptx::globaltimer_ns();                  \
+    } while (0)
+#else
+#define FL_SUM_TIME(slot)                                                                                               \
+    do {                                                                                                               \
+    } while (0)
+#endif
+    FL_SUM_TIME(0);
     ptx::grid_launch_dependents();
-    ptx::grid_dependency_wait();
+    if (stream_ordered)
+        ptx::grid_dependency_wait();
     __shared__ int s_ok;
     if (threadIdx.x == 0)
         s_ok = 1;
@@ -968,12 +1073,12 @@ __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, l
     bool      mine_ok     = true;
     uint64_t  t0          = 0;
     for (int f = threadIdx.x; f < total_flags && mine_ok; f += blockDim.x) {
-        const volatile unsigned int* flag = flags + static_cast<long long>(f / flags_per_rank) * flag_stride + f % flags_per_rank;
+        const unsigned int* flag = flags + static_cast<long long>(f / flags_per_rank) * flag_stride + f % flags_per_rank;
         for (uint32_t it = 1;; ++it) {
             // flags only ever grow (one step per call): "reached" = not behind, also across the 32-bit wrap
-            if (static_cast<int>(*flag - epoch) >= 0)
+            if (static_cast<int>(ptx::ld_relaxed_sys_u32(flag) - epoch) >= 0)
                 break;
-            __nanosleep(100);
+            __nanosleep(64);
             if ((it & 255u) == 0u) {
                 const uint64_t now = ptx::globaltimer_ns();
                 if (t0 == 0)
@@ -984,11 +1089,14 @@ __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, l
                 }
             }
         }
+        // the acquire that pairs with the sender's release of this flag: its partial sums are visible from here on
+        (void)ptx::ld_acquire_sys_u32(flag);
     }
     if (!mine_ok)
         s_ok = 0;
-    __threadfence_system();  // the flags were observed: the peers' stores before them are visible to the loads below
-    __syncthreads();
+    FL_SUM_TIME(1);
+    __syncthreads();  // every thread of the CTA is now ordered after all the flags the CTA's threads acquired
+    FL_SUM_TIME(2);
     if (!s_ok) {
         if (threadIdx.x == 0)
             atomicOr(status, kStatusPeerWaitExpired);
@@ -1013,6 +1121,7 @@ __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, l
     oh[2]        = finish_output(acc.z, bias, m + 2, activation, residual, static_cast<size_t>(i4) + 2);
     oh[3]        = finish_output(acc.w, bias, m + 3, activation, residual, static_cast<size_t>(i4) + 3);
     *reinterpret_cast<uint2*>(C + i4) = o;
+    FL_SUM_TIME(3);
 }
 
 }  // namespace flashllm

@@ -40,8 +40,12 @@ enum PlanField {
     kPlanScatterWarps,    // warps that decompress tiles, one whole tile per warp at a time (4..12, <= a_stages)
     kPlanProducers,       // warps issuing the bulk copies
     kPlanPath,            // how compressed words reach the scatter warps: kPathRing or kPathDirect
+    kPlanReduce,          // who adds workspace parts up: kReduceSecondKernel or kReduceLastCta
     kPlanFieldCount
 };
+
+constexpr int kReduceSecondKernel = 1;  // splitk_reduce_f32_kernel after the SpMM kernel
+constexpr int kReduceLastCta      = 2;  // inside the SpMM kernel, by the last CTA of each output tile to finish
 
 constexpr int kPathRing   = 1;  // bulk copies into a shared-memory ring (spmm_tcgen05_kernel)
 constexpr int kPathDirect = 2;  // global loads into the scatter warps' registers (spmm_tcgen05_direct_kernel)
@@ -58,6 +62,7 @@ struct SpmmPlan {
     int chunk_vectors;
     int scatter_warps;
     int producers;
+    int reduce;          // kReduceSecondKernel or kReduceLastCta (meaningful when workspace_k > 1)
     int offsets_staged;  // TileOffsets entries a CTA may stage in shared memory (0 = read them from global memory)
     int smem_bytes;      // dynamic shared memory of the launch
 };

@@ -92,15 +92,15 @@ int main(int argc, char** argv)
     const int   M = atoi(argv[1]), K = atoi(argv[2]), N = atoi(argv[3]), sparsity_pct = atoi(argv[4]), split_k = atoi(argv[5]);
     // optional, in any order after the five numbers: --ref <reference .so>, --plan name=value[,name=value...]
     // (the fields of FlashLLM_SetPlan: cluster_k, workspace_k, a_stages, b_stages, b_batch, ring_slots, chunk_vectors,
-    // scatter_warps, producers, path)
+    // scatter_warps, producers, path, reduce)
     const char* ref_path = nullptr;
     for (int a = 6; a + 1 < argc; a += 2) {
         if (strcmp(argv[a], "--ref") == 0)
             ref_path = argv[a + 1];
         else if (strcmp(argv[a], "--plan") == 0) {
-            static const char* names[10] = {"cluster_k",  "workspace_k",   "a_stages",      "b_stages",  "b_batch",
-                                            "ring_slots", "chunk_vectors", "scatter_warps", "producers", "path"};
-            int                fields[10] = {0};
+            static const char* names[11] = {"cluster_k",  "workspace_k",   "a_stages",      "b_stages",  "b_batch", "ring_slots",
+                                            "chunk_vectors", "scatter_warps", "producers", "path", "reduce"};
+            int                fields[11] = {0};
             std::string        spec(argv[a + 1]);
             size_t             pos = 0;
             while (pos < spec.size()) {
@@ -108,7 +108,7 @@ int main(int argc, char** argv)
                 const std::string item = spec.substr(pos, end == std::string::npos ? std::string::npos : end - pos);
                 const size_t eq = item.find('=');
                 bool known = false;
-                for (int f = 0; f < 10 && eq != std::string::npos; ++f)
+                for (int f = 0; f < 11 && eq != std::string::npos; ++f)
                     if (item.compare(0, eq, names[f]) == 0) {
                         fields[f] = atoi(item.c_str() + eq + 1);
                         known     = true;
@@ -119,7 +119,7 @@ int main(int argc, char** argv)
                 }
                 pos = end == std::string::npos ? spec.size() : end + 1;
             }
-            FlashLLM_SetPlan(fields, 10);
+            FlashLLM_SetPlan(fields, 11);
         }
         else {
             printf("unknown option %s\n", argv[a]);

@@ -288,7 +288,7 @@ void FlashLLM_SetLaunchOverlap(int enable);
 
 /* Tuning hook replacing the reference's compile-time TilingConfig<...> choice (csrc/TilingConfig.h:36-52,
  * csrc/SpMM_API.cu:79-118): fixes launch-plan fields for subsequent calls from this process.  `fields` holds up to
- * ten ints, 0 = choose automatically, in this order:
+ * eleven ints, 0 = choose automatically, in this order:
  *   0 cluster_k       K parts summed inside a thread-block cluster through distributed shared memory (1..8)
  *   1 workspace_k     extra K parts through Reduction_Workspace (capped at Split_K/2 of the call: an fp32 partial
  *                     matrix takes the room of two fp16 ones)
@@ -302,10 +302,17 @@ void FlashLLM_SetLaunchOverlap(int enable);
  *   9 path            1 = ring form: the compressed stream is copied into a shared-memory ring by bulk copies;
  *                     2 = register-streaming form (the default): scatter warps load their tiles' words from global
  *                     memory into registers, tiles alternate between two MMA-issuing threads
+ *  10 reduce          who adds the workspace parts up: 1 = a second kernel (the default; with launch overlap it
+ *                     hides behind the neighbouring SpMMs); 2 = the SpMM kernel itself: every CTA parks its fp32
+ *                     partial tile and counts itself in on a counter of the output tile, the CTA that completes the
+ *                     count adds the parts in part order and finishes the output (nobody waits; same bits as 1; the
+ *                     counters belong to the library, one set per stream, 32 streams per device -- a 33rd stream, or a
+ *                     call with more than 2048 output tiles, gets the second kernel).  The fused all-reduce always
+ *                     uses 2 for its own K split.
  * FlashLLM_SetPlan(nullptr, 0) restores automatic choice. */
 void FlashLLM_SetPlan(const int* fields, int count);
 
-/* Describes the plan the next SpMM call with these sizes would use: out[0..9] as above, out[10] = dynamic shared
+/* Describes the plan the next SpMM call with these sizes would use: out[0..10] as above, out[11] = dynamic shared
  * memory in bytes; `count` = entries available in `out`. */
 int FlashLLM_GetPlan(int M, int N, int K, int Split_K, int* out, int count);
 

@@ -65,10 +65,44 @@ def test_dense_and_sparse_tiles_alternate_in_a_stage(lib, oracle, form):
 
 
 @pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
-@pytest.mark.parametrize("cluster_k,workspace_k,split_k", [(2, 1, 1), (4, 1, 1), (1, 3, 6), (2, 2, 4), (8, 1, 1)])
-def test_k_splits(lib, oracle, form, cluster_k, workspace_k, split_k):
+@pytest.mark.parametrize("reduce", [1, 2], ids=["second-kernel", "last-cta"])
+@pytest.mark.parametrize("cluster_k,workspace_k,split_k", [(2, 1, 1), (4, 1, 1), (1, 3, 6), (2, 2, 4), (8, 1, 1), (3, 1, 1),
+                                                           (5, 2, 4), (6, 1, 1), (7, 1, 1), (1, 32, 64), (1, 2, 5)])
+def test_k_splits(lib, oracle, form, reduce, cluster_k, workspace_k, split_k):
+    """Every way of cutting K: parts summed inside clusters of any size up to 8, workspace parts summed by the last
+    CTA of an output tile to finish or by the second kernel, and both at once."""
+    if workspace_k == 1 and reduce == 1:
+        pytest.skip("no workspace parts: the reduce mode does not matter")
     A, B = random_problem(lib, 256, 2048, 16, 0.8, 13)
-    _check(lib, oracle, A, B, 16, split_k, dict(cluster_k=cluster_k, workspace_k=workspace_k, **form), "K split")
+    _check(lib, oracle, A, B, 16, split_k,
+           dict(cluster_k=cluster_k, workspace_k=workspace_k, reduce=reduce, **form), "K split")
+
+
+@pytest.mark.parametrize("N", [16, 64, 256])
+def test_sum_by_last_cta_is_deterministic_and_leaves_its_counters_clean(lib, oracle, N):
+    """The order in which the CTAs of an output tile finish changes from launch to launch; the sum must not.  Repeated
+    launches on one stream reuse the same counters, which therefore have to be back at zero every time; a second
+    stream gets counters of its own."""
+    M, K, split_k = 1152, 4096, 16
+    A, B = random_problem(lib, M, K, N, 0.8, 77 + N)
+    comp, offs, _ = lib.InitSparseMatrixA_API(A)
+    want = oracle.gemm_f32(A, B)
+    lib.set_plan(cluster_k=1, workspace_k=8, reduce=2)
+    try:
+        prob = DeviceProblem(lib, comp, offs, B, M, N, K, split_k)
+        first = prob.run().copy()
+        assert_close(first, want, f"N={N}")
+        for _ in range(20):
+            assert np.array_equal(prob.run(), first)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            assert np.array_equal(prob.run(), first)
+        second_kernel = None
+        lib.set_plan(cluster_k=1, workspace_k=8, reduce=1)
+        second_kernel = prob.run().copy()
+    finally:
+        lib.set_plan()
+    assert np.array_equal(second_kernel, first)  # both add the parts in part order from the same fp32 partial sums
 
 
 @pytest.mark.parametrize("form", FORMS, ids=FORM_IDS)
