@@ -323,6 +323,16 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr)
     return v;
 }
 
+__device__ __forceinline__ float4 ld_dsmem_v4_f32(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

@@ -392,20 +392,11 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                     ve2 = offs[j + WARPS + 1];
                 }
                 // ---- clear the stage (each sharing warp its part), then scatter the new tile
-#ifdef FLASHLLM_ZERO_BULK
-                // experiment: one bulk zero-initialising store per participating lane instead of 32 vector stores
-                if (lane < FLASHLLM_ZERO_BULK)
-                    asm volatile("st.bulk.weak.shared::cta [%0], %1, 0;" ::"r"(
-                                     stage + static_cast<uint32_t>(h * FLASHLLM_ZERO_BULK + lane) * (kDenseTileBytes / (FLASHLLM_ZERO_BULK * WPT))),
-                                 "l"(static_cast<unsigned long long>(kDenseTileBytes / (FLASHLLM_ZERO_BULK * WPT)))
-                                 : "memory");
-#else
                 if (!(FLASHLLM_ABLATE & 1)) {
 #pragma unroll
                     for (int q = 0; q < 32 / WPT; ++q)
                         sts_zero16(stage + static_cast<uint32_t>((q * WPT + h) * 32 + lane) * 16u);
                 }
-#endif
                 // another lane's (or the partner warp's) zero must not land on top of a new value
                 if (WPT == 1)
                     __syncwarp();
@@ -431,7 +422,6 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                 }
                 if (lane == 0)
                     FL_TRACE(5, j);
-#ifndef FLASHLLM_FETCH_FIRST
 #if !(FLASHLLM_ABLATE & 16)  // timing only: without the proxy fence the tensor core may read stale words
                 ptx::fence_proxy_async_smem();
 #endif
@@ -440,7 +430,6 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                     ptx::mbar_arrive(full_bar);
                 if (lane == 0)
                     FL_TRACE(6, j);
-#endif
                 // ---- start fetching the following tile
                 if (has_next) {
                     bad  = (ve2 < vb2) || (ve2 - vb2 > kMaxTileVectors) || (vb2 < 0);
@@ -456,14 +445,6 @@ __global__ void __launch_bounds__((1 + kDirectIssuers + WARPS * WPT) * 32, MIN_B
                             ptx::prefetch_l2_bulk(p.compressed + pb, static_cast<uint32_t>(pe - pb) * 16u);
                     }
                 }
-#ifdef FLASHLLM_FETCH_FIRST
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0)
-                    ptx::mbar_arrive(full_bar);
-                if (lane == 0)
-                    FL_TRACE(6, j);
-#endif
                 if (lane == 0)
                     FL_TRACE(13, j);
             }

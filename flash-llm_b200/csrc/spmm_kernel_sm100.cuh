@@ -365,36 +365,67 @@ __device__ __forceinline__ void accumulators_to_output(const SpmmParams& p, uint
 }
 
 // Between the two cluster barriers: every CTA of the cluster has parked its fp32 partial tile [N_TILE][128] at `base`
-// of its shared memory; CTA `rank` sums and stores its 1/S share of the tile through distributed shared memory.
+// of its shared memory; CTA `rank` sums and stores its 1/S share of the tile through distributed shared memory, four
+// neighbouring rows per thread.  The S remote loads of a thread are issued together and added in rank order.
 template<int N_TILE>
 __device__ __forceinline__ void cluster_reduce_store(const SpmmParams& p, uint32_t base, int rank, int S, int G, int g, int n_idx,
                                                      int tile_row, int tid, int threads, bool store_ok)
 {
     const int    n_valid  = (p.N - n_idx * N_TILE) < N_TILE ? (p.N - n_idx * N_TILE) : N_TILE;
-    const int    total    = N_TILE * kTileM;
-    const int    lo       = static_cast<int>(static_cast<long long>(total) * rank / S);
-    const int    hi       = static_cast<int>(static_cast<long long>(total) * (rank + 1) / S);
+    const int    quads    = N_TILE * (kTileM / 4);
+    const int    lo       = static_cast<int>(static_cast<long long>(quads) * rank / S);
+    const int    hi       = static_cast<int>(static_cast<long long>(quads) * (rank + 1) / S);
     const size_t tile_off = static_cast<size_t>(n_idx) * N_TILE * p.M + static_cast<size_t>(tile_row) * kTileM;
-    half* const  out_tile  = p.out + tile_off;
     float* const part_tile = G > 1 ? p.partial + static_cast<size_t>(g) * p.M * p.N + tile_off : nullptr;
+    const bool   wide_out  = (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;
+    uint32_t     peer[kMaxClusterK];
+#pragma unroll
+    for (int q = 0; q < kMaxClusterK; ++q)
+        peer[q] = q < S ? ptx::map_to_rank(base, q) : 0u;
     for (int e = lo + tid; e < hi; e += threads) {
-        const int n = e / kTileM, m = e % kTileM;
+        const int n = e / (kTileM / 4), m = (e % (kTileM / 4)) * 4;
         if (n >= n_valid)
             break;
-        float acc = 0.0f;
-        for (int q = 0; q < S; ++q)
-            acc += ptx::ld_dsmem_f32(ptx::map_to_rank(base + static_cast<uint32_t>(e) * 4u, q));
-        if (store_ok) {
-            if (part_tile)
-                part_tile[static_cast<size_t>(n) * p.M + m] = acc;
-            else if (p.push_world > 0) {
-                for (int w = 0; w < p.push_world; ++w)
-                    p.push_slot[w][tile_off + static_cast<size_t>(n) * p.M + m] = acc;
+        float4 v[kMaxClusterK];
+#pragma unroll
+        for (int q = 0; q < kMaxClusterK; ++q)
+            if (q < S)
+                v[q] = ptx::ld_dsmem_v4_f32(peer[q] + static_cast<uint32_t>(e) * 16u);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < kMaxClusterK; ++q)
+            if (q < S) {
+                acc.x += v[q].x;
+                acc.y += v[q].y;
+                acc.z += v[q].z;
+                acc.w += v[q].w;
             }
-            else
-                out_tile[static_cast<size_t>(n) * p.M + m] =
-                    finish_output(acc, p.bias, tile_row * kTileM + m, p.activation, p.residual,
-                                  tile_off + static_cast<size_t>(n) * p.M + m);
+        if (!store_ok)
+            continue;
+        const size_t at = static_cast<size_t>(n) * p.M + m;
+        if (part_tile)
+            *reinterpret_cast<float4*>(part_tile + at) = acc;
+        else if (p.push_world > 0) {
+            for (int w = 0; w < p.push_world; ++w)
+                *reinterpret_cast<float4*>(p.push_slot[w] + tile_off + at) = acc;
+        }
+        else {
+            const int row = tile_row * kTileM + m;
+            uint2     o;
+            half*     oh = reinterpret_cast<half*>(&o);
+            oh[0]        = finish_output(acc.x, p.bias, row, p.activation, p.residual, tile_off + at);
+            oh[1]        = finish_output(acc.y, p.bias, row + 1, p.activation, p.residual, tile_off + at + 1);
+            oh[2]        = finish_output(acc.z, p.bias, row + 2, p.activation, p.residual, tile_off + at + 2);
+            oh[3]        = finish_output(acc.w, p.bias, row + 3, p.activation, p.residual, tile_off + at + 3);
+            half* const dst = p.out + tile_off + at;
+            if (wide_out)
+                *reinterpret_cast<uint2*>(dst) = o;
+            else {
+                dst[0] = oh[0];
+                dst[1] = oh[1];
+                dst[2] = oh[2];
+                dst[3] = oh[3];
+            }
         }
     }
     if (part_tile != nullptr && p.tile_counters != nullptr)
@@ -459,12 +490,20 @@ __device__ __forceinline__ void splitk_sum_by_last_cta(const SpmmParams& p, int 
         const int    n  = q / (kTileM / 4), m = (q % (kTileM / 4)) * 4;
         const size_t at = tile_off + static_cast<size_t>(n) * p.M + m;
         float4       acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int g = 0; g < G; ++g) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(g) * count + at));
-            acc.x += v.x;
-            acc.y += v.y;
-            acc.z += v.z;
-            acc.w += v.w;
+        for (int g0 = 0; g0 < G; g0 += 4) {  // four parts' loads in flight at a time, added in part order
+            float4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (g0 + j < G)
+                    v[j] = __ldcg(reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(g0 + j) * count + at));
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (g0 + j < G) {
+                    acc.x += v[j].x;
+                    acc.y += v[j].y;
+                    acc.z += v[j].z;
+                    acc.w += v[j].w;
+                }
         }
         if (p.push_world > 0) {
             for (int w = 0; w < p.push_world; ++w)
@@ -515,14 +554,6 @@ __device__ __forceinline__ void scatter_vector(uint32_t stage, const uint4& w)
 // Zeroes one 16 KB stage with the 32 lanes of a scatter warp, fully unrolled: 32 stores of 16 bytes per lane.
 __device__ __forceinline__ void zero_fill_stage(uint32_t stage, int lane)
 {
-#ifdef FLASHLLM_ZERO_BULK
-    // one bulk zero-initialising store per lane group instead of per-lane vector stores
-    if (lane < FLASHLLM_ZERO_BULK)
-        asm volatile("st.bulk.weak.shared::cta [%0], %1, 0;" ::"r"(stage + lane * (kDenseTileBytes / FLASHLLM_ZERO_BULK)),
-                     "l"(static_cast<unsigned long long>(kDenseTileBytes / FLASHLLM_ZERO_BULK))
-                     : "memory");
-    return;
-#endif
 #pragma unroll
     for (int q = 0; q < kDenseTileBytes / (32 * 16); ++q)
         sts_zero16(stage + static_cast<uint32_t>(q * 32 + lane) * 16u);

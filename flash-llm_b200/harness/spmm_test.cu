@@ -86,11 +86,12 @@ static float time_spmm(SpmmFn fn, const uint4* nz, const int* offs, const half* 
 int main(int argc, char** argv)
 {
     if (argc < 6) {
-        printf("Wrong Inputs! Correct input format: ./spmm_test M K N Sparsity SplitK [--ref path/to/reference.so] [--plan name=value,...]\n");
+        printf("Wrong Inputs! Correct input format: ./spmm_test M K N Sparsity SplitK [--ref path/to/reference.so] [--plan name=value,...] [--overlap 0|1]\n");
         return 1;
     }
     const int   M = atoi(argv[1]), K = atoi(argv[2]), N = atoi(argv[3]), sparsity_pct = atoi(argv[4]), split_k = atoi(argv[5]);
-    // optional, in any order after the five numbers: --ref <reference .so>, --plan name=value[,name=value...]
+    // optional, in any order after the five numbers: --ref <reference .so>, --overlap 0|1 (launch overlap of
+    // consecutive SpMMs, off unless given), --plan name=value[,name=value...]
     // (the fields of FlashLLM_SetPlan: cluster_k, workspace_k, a_stages, b_stages, b_batch, ring_slots, chunk_vectors,
     // scatter_warps, producers, path, reduce)
     const char* ref_path = nullptr;
@@ -121,6 +122,8 @@ int main(int argc, char** argv)
             }
             FlashLLM_SetPlan(fields, 11);
         }
+        else if (strcmp(argv[a], "--overlap") == 0)
+            FlashLLM_SetLaunchOverlap(atoi(argv[a + 1]));
         else {
             printf("unknown option %s\n", argv[a]);
             return 1;
