@@ -65,7 +65,7 @@ COLD_BYTES = 512e6          # compressed bytes a GPU streams before an address r
 TIMED_REGION_S = 0.6        # the K timed steps are repeated until about this much device time has been measured
 # DRAM bytes (read + write) per algorithmic byte of the SpMM kernel, from one ncu capture of a half-height FFN1 case
 # (see profiles/); traffic grows with the rows, so a full launch is reported as this ratio times its algorithmic bytes.
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.024
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.018
 
 
 def measured_peak_gbs() -> tuple[float, str]:
