@@ -716,6 +716,7 @@ def run_tp_chain(args) -> None:
 
 
 def main() -> None:
+    global TIMED_REGION_S
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -728,7 +729,11 @@ def main() -> None:
     ap.add_argument("--workload", default="layer", choices=["layer", "tp-chain"],
                     help="layer: the four OPT-66B SpMMs, weight rows sharded, no collective (the headline metric); "
                          "tp-chain: the tensor-parallel layer chain with all-reduces")
+    ap.add_argument("--timed-seconds", type=float, default=TIMED_REGION_S,
+                    help="device time the repetitions of the K timed steps add up to (lower it for a profiler's launch "
+                         "list; the default is what a reported number needs)")
     args = ap.parse_args()
+    TIMED_REGION_S = args.timed_seconds
     if args.workload == "tp-chain" and args.impl == "ours":
         run_tp_chain(args)
     elif args.impl == "reference":
