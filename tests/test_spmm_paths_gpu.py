@@ -160,3 +160,23 @@ def test_n_beyond_one_mma_tile(lib, oracle, form, N):
     """N a multiple of 128 (the reference's large-N dispatch, csrc/SpMM_API.cu:97-112): several N tiles per tile row."""
     A, B = random_problem(lib, 256, 1024, N, 0.8, 500 + N)
     _check(lib, oracle, A, B, N, 4, dict(**form), f"N={N}")
+
+
+def test_more_streams_than_counter_sets_fall_back_to_the_second_kernel(lib, oracle):
+    """The in-kernel split-K sum binds a set of arrival counters to each stream it is used on (32 sets per device);
+    calls on further streams must still be right (they are summed by the second kernel)."""
+    M, K, N, split_k = 512, 2048, 16, 8
+    A, B = random_problem(lib, M, K, N, 0.8, 91)
+    comp, offs, _ = lib.InitSparseMatrixA_API(A)
+    want = oracle.gemm_f32(A, B)
+    prob = DeviceProblem(lib, comp, offs, B, M, N, K, split_k)
+    lib.set_plan(cluster_k=1, workspace_k=4, reduce=2)
+    try:
+        first = prob.run().copy()
+        assert_close(first, want, "default stream")
+        streams = [torch.cuda.Stream() for _ in range(40)]
+        for s_ in streams:
+            with torch.cuda.stream(s_):
+                assert np.array_equal(prob.run(), first)
+    finally:
+        lib.set_plan()
