@@ -217,7 +217,9 @@ static bool is_pow2(int v)
 // (kernel_benchmark/benchmark.sh:13-15).
 // `max_parts`: workspace parts the caller has room for (Split_K / 2 for a caller's Reduction_Workspace, whose Split_K
 // fp16 matrices hold half as many fp32 ones).
-static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int max_parts, SpmmPlan* out)
+// `sends`: the call is the sending half of a fused all-reduce, where workspace parts are always summed by the last
+// CTA of a tile, which then also stores the sum to every GPU.
+static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int max_parts, SpmmPlan* out, bool sends = false)
 {
     PlanOverride ov;
     {
@@ -264,7 +266,8 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int max
     // the number of clusters of S CTAs the GPU holds at a time -- measured, and well below slots/S for S >= 3 (71
     // clusters of 4, 33 of 8 on 296 slots): one cluster more than that and the launch takes twice as long.  Every
     // CTA processes k_tiles/(S*G) tiles after a fixed cost worth about 16 tiles; a cluster sum costs about 3 more,
-    // the sum by the last CTA 2 + 0.1 per part, a second kernel half a tile per part.  The cheapest (S, G) wins,
+    // the sum by the last CTA 2 + 0.1 per part (8 + 0.1 per part in a fused all-reduce, where the peers wait for that
+    // CTA: measured on 2 GPUs, 9216x1152 ... 9216x18432), a second kernel half a tile per part.  The cheapest (S, G) wins,
     // fewer parts on a tie.  Replaces the reference's hand-tuned Split_K tables (kernel_benchmark/benchmark.sh:13-15).
     static const int kClustersResident2[kMaxClusterK + 1] = {0, 296, 148, 92, 71, 56, 45, 37, 33};  // two CTAs per SM
     static const int kClustersResident1[kMaxClusterK + 1] = {0, 148, 74, 45, 33, 26, 22, 15, 15};   // one CTA per SM
@@ -278,7 +281,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int max
     // (measured on eleven shapes from 9216x1152 to 9216x36864: with launch overlap the second kernel hides behind its
     // neighbours and beats the sum by the last CTA, which sits on every tile's critical path, by ~2 us per call;
     // without overlap the two are level.  The fused all-reduce always sums by the last CTA: that CTA also sends.)
-    pl.reduce           = ov.v[kPlanReduce] ? ov.v[kPlanReduce] : kReduceSecondKernel;
+    pl.reduce           = sends ? kReduceLastCta : (ov.v[kPlanReduce] ? ov.v[kPlanReduce] : kReduceSecondKernel);
     if (ctas_flat > kCounterTiles)
         pl.reduce = kReduceSecondKernel;
     // (without launch overlap a second kernel costs a whole launch: small problems then do better with clusters alone)
@@ -293,7 +296,7 @@ static cudaError_t make_plan(const DeviceState* st, int M, int N, int K, int max
             const long long clusters = static_cast<long long>(ctas_flat) * g;
             const double    waves    = static_cast<double>((clusters + capacity(s_) - 1) / capacity(s_));
             const double    per_cta  = static_cast<double>((k_tiles + s_ * g - 1) / (s_ * g)) + 16.0 + (s_ > 1 ? 3.0 : 0.0)
-                                    + (g > 1 && pl.reduce == kReduceLastCta ? 2.0 + 0.1 * g : 0.0);
+                                    + (g > 1 && pl.reduce == kReduceLastCta ? (sends ? 8.0 : 2.0) + 0.1 * g : 0.0);
             const double cost = waves * per_cta + (g > 1 && pl.reduce == kReduceSecondKernel ? 0.5 * g : 0.0);
             if ((s_ == 1 && g == 1) || cost < best_cost - 1e-9
                 || (cost < best_cost + 1e-9 && s_ * g < best_s * best_g)) {
@@ -491,7 +494,8 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
         return err;
 
     SpmmParams params{};
-    if ((err = make_plan(st, M_Global, N_Global, K_Global, comm ? kCommLocalParts : Split_K / 2, &params.plan))
+    if ((err = make_plan(st, M_Global, N_Global, K_Global, comm ? kCommLocalParts : Split_K / 2, &params.plan,
+                         comm != nullptr))
         != cudaSuccess)
         return err;
     SpmmPlan& pl = params.plan;
