@@ -201,8 +201,12 @@ int FlashLLM_SpMM_SplitK_Epilogue(void*       stream,
  * reference's caller runs the SpMM and then FasterTransformer's NCCL all-reduce (third_party/ft.patch:2822-2846 and
  * the call sites :1328-1340, :615-633; its custom all-reduce is switched off, :97).  Here the SpMM kernel stores its
  * fp32 partial sums straight into a receive buffer on every GPU of the group (plain peer stores over NVLink) and
- * raises a flag per CTA; a second kernel on each GPU waits for all flags (bounded: 2 s unless set otherwise, then status
- * bit 32 and nothing is stored), adds the partial sums in rank order and rounds once, so every GPU ends with the same bits.
+ * raises a flag per CTA (per output tile when the GPU's own K range is cut into parts: the parts are parked in the GPU's
+ * own buffer and the last CTA of a tile to finish adds them up and sends the sum); a second kernel on each GPU waits for
+ * all flags (bounded: 2 s unless set otherwise, then status bit 32 and nothing is stored), adds the partial sums in rank
+ * order and rounds once, so every GPU ends with the same bits.  In the normal call the second kernel depends on the flags
+ * alone, not on the first kernel having drained; C is complete, as for any call, when the stream reaches the work
+ * enqueued after the call.
  * ---------------------------------------------------------------------------------------------------------- */
 
 /* Bytes of one GPU's receive buffer for a group of `world` (1..8) GPUs and outputs of up to `max_elems` = M*N values
@@ -229,9 +233,10 @@ int FlashLLM_Comm_SetWaitLimit(void* comm, int milliseconds);
 
 /* C[n][m] = act(sum over the group's GPUs w of sum_k A_w[m][k] * B_w[n][k] + bias[m]) + residual[n][m] on every GPU
  * (`residual`: this GPU's copy of the layer input, or nullptr).  Arguments as FlashLLM_SpMM_SplitK_Epilogue without
- * workspace and Split_K (the K cut of one GPU's product stays inside thread-block
- * clusters).  `phases`: 3 = both kernels (the normal call); 1 = the SpMM and its stores only, 2 = the summing kernel
- * only -- for a host that drives several GPUs' calls from one thread and wants all sends enqueued before any sum. */
+ * workspace and Split_K (the library cuts K itself: cluster parts, and up to 8 parts parked in the communicator's
+ * buffer).  `phases`: 3 = both kernels (the normal call); 1 = the SpMM and its stores only, 2 = the summing kernel
+ * only, ordered after everything enqueued before it -- for a host that drives several GPUs' calls, or several ranks
+ * emulated on one GPU, from one thread and wants all sends enqueued before any sum. */
 int FlashLLM_SpMM_SplitK_AllReduce(void*       comm,
                                    void*       stream,
                                    const void* Compressed_A,
