@@ -471,6 +471,9 @@ __device__ __forceinline__ void splitk_sum_by_last_cta(const SpmmParams& p, int 
         // arrivals in the low half of the counter; a CTA that gave up also marks the high half, so that the last one
         // knows the tile's sum is not to be trusted
         const unsigned int mine = *abort_flag == 0u ? 1u : 0x10001u;
+        // The counters and the parts may still be in use by the launch before this one on the stream until it has
+        // completed; a CTA that did no work has not waited for that yet (for the others this returns at once).
+        ptx::grid_dependency_wait();
         __threadfence();
         const unsigned int before = atomicAdd(p.tile_counters + tile_id, mine);
         const bool         last   = (before & 0xFFFFu) + 1u == static_cast<unsigned int>(arrivals);
