@@ -601,8 +601,8 @@ static cudaError_t spmm_launch_all(cudaStream_t stream,
         count_launch();
         return cudaLaunchKernelEx(&cfg, allreduce_sum_kernel, C, reinterpret_cast<const float*>(mine + set_slots),
                                   comm->max_elems, reinterpret_cast<const unsigned int*>(mine + set_flags), kCommFlagsPerRank,
-                                  comm->epoch, comm->world, comm_flags, count, bias, M_Global, activation, residual, st->status,
-                                  comm->wait_limit_ns, phases == 3 ? 0 : 1);
+                                  comm->epoch, comm->world, pl.workspace_k > 1 ? 1 : pl.cluster_k, tile_rows, pl.n_tile, count, bias,
+                                  M_Global, activation, residual, st->status, comm->wait_limit_ns, phases == 3 ? 0 : 1);
     }
     if (pl.workspace_k > 1 && pl.reduce == kReduceSecondKernel)
         return reduce_partials(stream, C, params.partial, static_cast<long long>(M_Global) * N_Global, pl.workspace_k,

@@ -1069,10 +1069,12 @@ constexpr unsigned kStatusPeerWaitExpired = 32u;  // a GPU of the group did not 
 
 // Fused all-reduce, receiving side: C = fp16(act(sum over the group's GPUs of their fp32 partial products + bias)).
 // `slots` holds `world` matrices [N][M] fp32, `slot_stride` floats apart (slot w written by GPU w); `flags` holds, for
-// each sender, `flag_stride` words of which the first `flags_per_rank` are in use (one per CTA or per output tile of
-// the sending grid).  Before a CTA reads anything it waits, for at most `wait_limit_ns`, until every flag of every
-// sender has reached `epoch` (a sender raises a flag after the stores it stands for, so all of them together cover the
-// whole matrix).  Slots are added in rank order on every GPU, so all GPUs get the same bits.
+// each sender, `flag_stride` words: `flags_per_tile` consecutive ones per output tile (tile index = N tile *
+// tile_rows + tile row), one per CTA that stored a piece of the tile (a cluster's CTAs), or one for the tile when the
+// last CTA of a tile sent its sum.  A warp covers 128 consecutive outputs = one row segment of ONE output tile, so it
+// waits only for that tile's flags: lane l polls flag l % flags_per_tile of sender l / flags_per_tile (at most
+// 8 senders x 8 flags, two per lane), for at most `wait_limit_ns`.  A sender raises a flag after the stores it stands
+// for.  Slots are added in rank order on every GPU, so all GPUs get the same bits.
 // `stream_ordered` != 0: the kernel first waits for everything enqueued before it on its stream (needed when the
 // senders are kernels of the same stream on the same GPU: nothing else guarantees that they run at all while this
 // one polls).  With 0 the flags are the only dependency: this GPU's sender is the launch right before, all of whose
@@ -1080,8 +1082,9 @@ constexpr unsigned kStatusPeerWaitExpired = 32u;  // a GPU of the group did not 
 // kernel then neither waits for its predecessor to drain nor for its peer stores to be flushed.
 __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, long long slot_stride,
                                      const unsigned int* flags, int flag_stride, unsigned int epoch, int world,
-                                     int flags_per_rank, long long count, const half* __restrict__ bias, int M,
-                                     int activation, const half* __restrict__ residual, unsigned int* status,
+                                     int flags_per_tile, int tile_rows, int n_tile, long long count,
+                                     const half* __restrict__ bias, int M, int activation,
+                                     const half* __restrict__ residual, unsigned int* status,
                                      unsigned long long wait_limit_ns, int stream_ordered)
 {
 #ifdef FLASHLLM_CTA_TIMES
@@ -1099,18 +1102,24 @@ __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, l
     ptx::grid_launch_dependents();
     if (stream_ordered)
         ptx::grid_dependency_wait();
-    __shared__ int s_ok;
-    if (threadIdx.x == 0)
-        s_ok = 1;
-    __syncthreads();
-    const int total_flags = world * flags_per_rank;
-    bool      mine_ok     = true;
-    uint64_t  t0          = 0;
-    for (int f = threadIdx.x; f < total_flags && mine_ok; f += blockDim.x) {
-        const unsigned int* flag = flags + static_cast<long long>(f / flags_per_rank) * flag_stride + f % flags_per_rank;
+    const long long i4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i4 - (threadIdx.x & 31) * 4 >= count)  // the whole warp lies past the end (count is a multiple of 128)
+        return;
+    const int lane = threadIdx.x & 31;
+    const int n    = static_cast<int>(i4 / M);
+    const int m    = static_cast<int>(i4 % M);
+    const int tile = (n / n_tile) * tile_rows + m / kTileM;  // the same for all lanes of the warp
+    const int mine = world * flags_per_tile;                  // flags this warp depends on (<= 64)
+    bool      ok   = true;
+    uint64_t  t0   = 0;
+    for (int f = lane; f < mine && ok; f += 32) {
+        const unsigned int* flag =
+            flags + static_cast<long long>(f / flags_per_tile) * flag_stride + tile * flags_per_tile + f % flags_per_tile;
         for (uint32_t it = 1;; ++it) {
-            // flags only ever grow (one step per call): "reached" = not behind, also across the 32-bit wrap
-            if (static_cast<int>(ptx::ld_relaxed_sys_u32(flag) - epoch) >= 0)
+            // the acquire pairs with the sender's release of this flag: once the flag has reached this call's number,
+            // the sender's partial sums are visible.  Flags only ever grow (one step per call): "reached" = not
+            // behind, also across the 32-bit wrap.
+            if (static_cast<int>(ptx::ld_acquire_sys_u32(flag) - epoch) >= 0)
                 break;
             __nanosleep(64);
             if ((it & 255u) == 0u) {
@@ -1118,42 +1127,40 @@ __global__ void allreduce_sum_kernel(half* __restrict__ C, const float* slots, l
                 if (t0 == 0)
                     t0 = now;
                 else if (now - t0 > wait_limit_ns) {
-                    mine_ok = false;
+                    ok = false;
                     break;
                 }
             }
         }
-        // the acquire that pairs with the sender's release of this flag: its partial sums are visible from here on
-        (void)ptx::ld_acquire_sys_u32(flag);
     }
-    if (!mine_ok)
-        s_ok = 0;
     FL_SUM_TIME(1);
-    __syncthreads();  // every thread of the CTA is now ordered after all the flags the CTA's threads acquired
+    ok = __all_sync(0xFFFFFFFFu, ok);  // also orders every lane of the warp after the flags its lanes acquired
     FL_SUM_TIME(2);
-    if (!s_ok) {
-        if (threadIdx.x == 0)
+    if (!ok) {
+        if (lane == 0)
             atomicOr(status, kStatusPeerWaitExpired);
-        return;  // nothing is stored: the caller reads the status word
+        return;  // nothing is stored for this tile row segment: the caller reads the status word
     }
-    const long long i4 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
-    if (i4 >= count)
-        return;
+    float4 v[kMaxPushWorld];
+#pragma unroll
+    for (int w = 0; w < kMaxPushWorld; ++w)  // all senders' values requested together, added in rank order
+        if (w < world)
+            v[w] = __ldcg(reinterpret_cast<const float4*>(slots + static_cast<long long>(w) * slot_stride + i4));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int w = 0; w < world; ++w) {
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(slots + static_cast<long long>(w) * slot_stride + i4));
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-    }
-    const int m = static_cast<int>(i4 % M);
-    uint2     o;
-    half*     oh = reinterpret_cast<half*>(&o);
-    oh[0]        = finish_output(acc.x, bias, m, activation, residual, static_cast<size_t>(i4));
-    oh[1]        = finish_output(acc.y, bias, m + 1, activation, residual, static_cast<size_t>(i4) + 1);
-    oh[2]        = finish_output(acc.z, bias, m + 2, activation, residual, static_cast<size_t>(i4) + 2);
-    oh[3]        = finish_output(acc.w, bias, m + 3, activation, residual, static_cast<size_t>(i4) + 3);
+#pragma unroll
+    for (int w = 0; w < kMaxPushWorld; ++w)
+        if (w < world) {
+            acc.x += v[w].x;
+            acc.y += v[w].y;
+            acc.z += v[w].z;
+            acc.w += v[w].w;
+        }
+    uint2 o;
+    half* oh = reinterpret_cast<half*>(&o);
+    oh[0]    = finish_output(acc.x, bias, m, activation, residual, static_cast<size_t>(i4));
+    oh[1]    = finish_output(acc.y, bias, m + 1, activation, residual, static_cast<size_t>(i4) + 1);
+    oh[2]    = finish_output(acc.z, bias, m + 2, activation, residual, static_cast<size_t>(i4) + 2);
+    oh[3]    = finish_output(acc.w, bias, m + 3, activation, residual, static_cast<size_t>(i4) + 3);
     *reinterpret_cast<uint2*>(C + i4) = o;
     FL_SUM_TIME(3);
 }
