@@ -180,3 +180,31 @@ def test_more_streams_than_counter_sets_fall_back_to_the_second_kernel(lib, orac
                 assert np.array_equal(prob.run(), first)
     finally:
         lib.set_plan()
+
+
+@pytest.mark.parametrize("plan", [dict(cluster_k=1), dict(cluster_k=2), dict(cluster_k=1, workspace_k=4),
+                                  dict(cluster_k=1, workspace_k=4, reduce=2)], ids=["plain", "cluster", "parts", "parts-last-cta"])
+@pytest.mark.parametrize("offset_halves", [1, 2, 3])
+def test_output_that_is_only_two_byte_aligned(lib, oracle, plan, offset_halves):
+    """The reference interface asks nothing of C's alignment beyond that of a half; the wide stores of the cluster sum
+    and of the sums over workspace parts must give way to narrow ones (or to an uncut launch) for such a C."""
+    M, K, N, split_k = 256, 2048, 16, 8
+    A, B = random_problem(lib, M, K, N, 0.8, 97)
+    comp, offs, _ = lib.InitSparseMatrixA_API(A)
+    want = oracle.gemm_f32(A, B)
+    dev = torch.device("cuda:0")
+    comp_d = torch.from_numpy(np.ascontiguousarray(comp.view(np.int32))).to(dev)
+    offs_d, B_d = torch.from_numpy(offs).to(dev), torch.from_numpy(B).to(dev)
+    backing = torch.full((N * M + 8,), float("nan"), dtype=torch.float16, device=dev)
+    C = backing[offset_halves:offset_halves + N * M]
+    ws = torch.empty((split_k, N, M), dtype=torch.float16, device=dev)
+    lib.set_plan(**plan)
+    try:
+        lib.SpMM_SplitK_API(torch.cuda.current_stream().cuda_stream, None, comp_d.data_ptr(), offs_d.data_ptr(),
+                            B_d.data_ptr(), C.data_ptr(), M, N, K, ws.data_ptr(), split_k)
+        torch.cuda.synchronize()
+    finally:
+        lib.set_plan()
+    assert lib.consume_status() == 0
+    assert_close(C.view(N, M).cpu().numpy(), want, f"C at +{2 * offset_halves} bytes, plan {plan}")
+    assert torch.isnan(backing[:offset_halves]).all() and torch.isnan(backing[offset_halves + N * M:]).all()
